@@ -1,0 +1,77 @@
+/* C ABI of libb200mixers.so: sequence-mixing and normalisation kernels for decoder layers that are not plain softmax
+ * attention -- Dynamic-Tanh normalisation fused with the residual update, sliding-window attention with sigmoid weights,
+ * short causal convolutions, the gated delta rule and gated linear attention recurrences, PolyNorm, gated RMS output norm,
+ * soft-capped logits.  All pointers are device pointers; every function enqueues on `stream` and returns 0 or a cudaError_t.
+ *
+ * dtype: 0 = float, 1 = bfloat16, 2 = half: the type of activations AND of parameters (a model lives in one type).
+ * Whatever the dtype, the residual stream, attention scores and weights, every normalisation and everything inside a
+ * recurrence (state, decays, gates, unit vectors) are 32-bit floats.
+ *
+ * Batches: a row holds S new tokens that follow the tokens of earlier calls; `slot0` numbers the first new token's slot
+ * (the same for all rows) and `pad[b]` is row b's left padding: its token in slot c has position c - pad[b] and does not
+ * exist when that is negative. */
+#ifndef B200_MIXERS_H
+#define B200_MIXERS_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+typedef struct CUstream_st* mixers_stream_t;
+
+/* x[n, :] = float(table[ids[n], :]) */
+int mixers_embed_rows(int dtype, const void* table, const int64_t* ids, long n_rows, int width, float* x, mixers_stream_t stream);
+
+/* x += tanh(post_alpha * y) * post_w + post_b   (if y);   x += add (if add);   out = tanh(pre_alpha * x) * pre_w + pre_b (if out).
+ * x: float [n_rows, width], updated in place; y, out: dtype [n_rows, width]; vectors [width]; alphas: one element each. */
+int mixers_dyt_residual_norm(int dtype, float* x, long n_rows, int width, const void* y, const void* post_w, const void* post_b,
+                             const void* post_alpha, const void* add, const void* pre_w, const void* pre_b, const void* pre_alpha,
+                             void* out, mixers_stream_t stream);
+
+/* Queries, keys and values of new tokens taken from the columns of one projection output `proj` [B, S, ld]: per-head RMS norm
+ * (weights q_w / k_w [dim]), rotation of the pairs (2i, 2i+1), i < rot_dims / 2, by position * inv_freq[i]; queries go to
+ * q_out float [B, S, heads, dim], keys and values into the caches k_store [B, kv_heads, cap, dim] / v_store [.., vdim] at
+ * storage index held + t.  The token at storage index j sits in slot j + shift. */
+int mixers_window_qk_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads,
+                             int kv_heads, int dim, int vdim, const void* q_w, const void* k_w, float eps, const float* inv_freq,
+                             int rot_dims, float* q_out, void* k_store, void* v_store, int cap, int held, int shift,
+                             const int32_t* pad, mixers_stream_t stream);
+
+/* out[b, t, out_col + h * vdim + :] = out_scale * sum_j sigmoid(q . k_j * scale + head_bias[h]) v_j over the keys j of the same
+ * row with 0 <= c - j < window (c = held + t the query's own storage index) that are not padding.  out: dtype [B * S, ld_out]. */
+int mixers_sigmoid_window_attention(int dtype, const float* q, const void* k_store, const void* v_store, int B, int S, int heads,
+                                    int kv_heads, int dim, int vdim, int cap, int held, int shift, const int32_t* pad, int window,
+                                    float scale, const void* head_bias, void* out, int ld_out, int out_col, float out_scale,
+                                    mixers_stream_t stream);
+
+/* y[b, t, c] = silu(sum_j w[c, j] * in(t - taps + 1 + j)): in(t') = proj[b, t', off + c] for a new token, tail[b, taps-1+t', c]
+ * for t' < 0, zero for padding.  tail_next receives the last taps-1 inputs.  w: [C, taps]; tails: [B, max(taps-1,1), C]. */
+int mixers_short_conv_silu(int dtype, const void* proj, int B, int S, int ld, int off, int C, int taps, const void* w,
+                           const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream);
+
+/* Gated delta rule.  conv [B, S, C]: q | k (kv_heads x dim each) | v (heads x vdim) after the short convolution; q and k are
+ * made unit vectors here (q also times dim^-1/2).  beta = sigmoid(proj[.., off_b + h]), decay = exp(-exp(A_log[h]) *
+ * softplus(proj[.., off_a + h] + dt_bias[h])).  Per head:  M <- decay M;  u = beta (v - M^T k);  M <- M + k u^T;  o = M^T q.
+ * state: float [B, heads, dim, vdim], updated in place; o: float [B, S, heads, vdim]. */
+int mixers_gated_delta_rule(int dtype, const void* conv, int B, int S, int kv_heads, int heads, int dim, int vdim,
+                            const void* proj, int ld, int off_b, int off_a, const void* A_log, const void* dt_bias, float* state,
+                            int slot0, const int32_t* pad, float* o, mixers_stream_t stream);
+
+/* Gated linear attention.  proj [B, S, ld]: q | k (heads x dim each) | v (heads x vdim) from column 0; z [B, S, heads * dim]:
+ * decay logits, alpha = sigmoid(z)^(1/tau).  Per head:  M <- diag(alpha) M + k v^T;  o = M^T (q dim^-1/2). */
+int mixers_gated_linear_attention(int dtype, const void* proj, int B, int S, int ld, int heads, int dim, int vdim, const void* z,
+                                  float tau, float* state, int slot0, const int32_t* pad, float* o, mixers_stream_t stream);
+
+/* out[n, out_col + h * vdim + c] = out_scale * o[n, h, c] / rms(o[n, h, :]) * w[c] * silu(gate[n, off_g + h * vdim + c]) */
+int mixers_gated_rms_norm(int dtype, const float* o, long n_rows, int heads, int vdim, const void* gate, int ld_gate, int off_g,
+                          const void* w, float eps, void* out, int ld_out, int out_col, float out_scale, mixers_stream_t stream);
+
+/* out = a N(z) + b N(z^2) + c N(z^3) + e, N(v) = v / rms(v) over a row; coef = {a, b, c, e} */
+int mixers_poly_norm(int dtype, const void* z, long n_rows, int width, const void* coef, float eps, void* out, mixers_stream_t stream);
+
+/* out = cap * tanh(x / cap) as floats (cap <= 0: a plain conversion) */
+int mixers_soft_cap(int dtype, const void* x, long n, float cap, float* out, mixers_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

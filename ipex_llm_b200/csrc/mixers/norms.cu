@@ -1,0 +1,130 @@
+// Normalisations and other row-wise pieces: embedding gather into the 32-bit residual stream, Dynamic Tanh fused with the
+// residual update, gated RMS output norm of the recurrences, PolyNorm, soft-capped logits.  All of them are bound by memory
+// traffic: one pass over their rows, arithmetic in 32-bit floats.
+#include "mixers_common.cuh"
+
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids, long n_rows, int width, float* __restrict__ x) {
+    long total = n_rows * (long)width;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        long n = i / width;
+        int c = (int)(i - n * width);
+        x[i] = to_f(table[ids[n] * (long)width + c]);
+    }
+}
+
+template <typename T>
+__global__ void dyt_residual_norm_kernel(float* __restrict__ x, long n_rows, int width, const T* __restrict__ y, const T* __restrict__ post_w,
+                                         const T* __restrict__ post_b, const T* __restrict__ post_alpha, const T* __restrict__ add,
+                                         const T* __restrict__ pre_w, const T* __restrict__ pre_b, const T* __restrict__ pre_alpha,
+                                         T* __restrict__ out) {
+    const float pa = y ? to_f(post_alpha[0]) : 0.0f;
+    const float a = out ? to_f(pre_alpha[0]) : 0.0f;
+    long total = n_rows * (long)width;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        int c = (int)(i % width);
+        float v = x[i];
+        if (y) v += tanhf(pa * to_f(y[i])) * to_f(post_w[c]) + to_f(post_b[c]);
+        if (add) v += to_f(add[c]);
+        if (y || add) x[i] = v;
+        if (out) out[i] = from_f<T>(tanhf(a * v) * to_f(pre_w[c]) + to_f(pre_b[c]));
+    }
+}
+
+// one warp per (row, head)
+template <typename T>
+__global__ void gated_rms_norm_kernel(const float* __restrict__ o, long n_rows, int heads, int vdim, const T* __restrict__ gate, int ld_gate,
+                                      int off_g, const T* __restrict__ w, float eps, T* __restrict__ out, int ld_out, int out_col, float out_scale) {
+    long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (warp >= n_rows * heads) return;
+    long n = warp / heads;
+    int h = (int)(warp - n * heads);
+    const float* src = o + warp * (long)vdim;
+    float ss = 0.0f;
+    for (int c = lane; c < vdim; c += 32) { float v = src[c]; ss += v * v; }
+    ss = warp_sum(ss);
+    float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    const T* g = gate + n * (long)ld_gate + off_g + h * vdim;
+    T* dst = out + n * (long)ld_out + out_col + h * vdim;
+    for (int c = lane; c < vdim; c += 32)
+        dst[c] = from_f<T>(src[c] * inv * to_f(w[c]) * silu_f(to_f(g[c])) * out_scale);
+}
+
+// one block per row
+template <typename T>
+__global__ void poly_norm_kernel(const T* __restrict__ z, long n_rows, int width, const T* __restrict__ coef, float eps, T* __restrict__ out) {
+    __shared__ float red[3][32];
+    long n = blockIdx.x;
+    const T* src = z + n * (long)width;
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = to_f(src[c]);
+        float v2 = v * v;
+        s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2;
+    }
+    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);
+    int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { red[0][wid] = s2; red[1][wid] = s4; red[2][wid] = s6; }
+    __syncthreads();
+    s2 = s4 = s6 = 0.0f;
+    for (int i = 0; i < nw; ++i) { s2 += red[0][i]; s4 += red[1][i]; s6 += red[2][i]; }      // same order in every thread
+    float r1 = 1.0f / sqrtf(s2 / (float)width + eps), r2 = 1.0f / sqrtf(s4 / (float)width + eps), r3 = 1.0f / sqrtf(s6 / (float)width + eps);
+    float a = to_f(coef[0]) * r1, b = to_f(coef[1]) * r2, cc = to_f(coef[2]) * r3, e = to_f(coef[3]);
+    T* dst = out + n * (long)width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = to_f(src[c]);
+        dst[c] = from_f<T>(a * v + b * (v * v) + cc * (v * v * v) + e);
+    }
+}
+
+template <typename T>
+__global__ void soft_cap_kernel(const T* __restrict__ x, long n, float cap, float* __restrict__ out) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        float v = to_f(x[i]);
+        out[i] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+    }
+}
+
+static inline int grid_for(long total, int block) {
+    long g = (total + block - 1) / block;
+    return (int)(g < 1 ? 1 : (g > 148L * 32 ? 148L * 32 : g));
+}
+
+extern "C" int mixers_embed_rows(int dtype, const void* table, const int64_t* ids, long n_rows, int width, float* x, mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    MIXERS_DISPATCH(dtype, embed_rows_kernel<T><<<grid_for(n_rows * width, 256), 256, 0, (cudaStream_t)stream>>>((const T*)table, ids, n_rows, width, x));
+    return mixers_status();
+}
+
+extern "C" int mixers_dyt_residual_norm(int dtype, float* x, long n_rows, int width, const void* y, const void* post_w, const void* post_b,
+                                        const void* post_alpha, const void* add, const void* pre_w, const void* pre_b, const void* pre_alpha,
+                                        void* out, mixers_stream_t stream) {
+    if (n_rows <= 0 || (!y && !add && !out)) return 0;
+    MIXERS_DISPATCH(dtype, dyt_residual_norm_kernel<T><<<grid_for(n_rows * width, 256), 256, 0, (cudaStream_t)stream>>>(
+        x, n_rows, width, (const T*)y, (const T*)post_w, (const T*)post_b, (const T*)post_alpha, (const T*)add, (const T*)pre_w,
+        (const T*)pre_b, (const T*)pre_alpha, (T*)out));
+    return mixers_status();
+}
+
+extern "C" int mixers_gated_rms_norm(int dtype, const float* o, long n_rows, int heads, int vdim, const void* gate, int ld_gate, int off_g,
+                                     const void* w, float eps, void* out, int ld_out, int out_col, float out_scale, mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    long warps = n_rows * heads;
+    int blocks = (int)((warps + 3) / 4);
+    MIXERS_DISPATCH(dtype, gated_rms_norm_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(o, n_rows, heads, vdim, (const T*)gate, ld_gate, off_g,
+                                                                                                (const T*)w, eps, (T*)out, ld_out, out_col, out_scale));
+    return mixers_status();
+}
+
+extern "C" int mixers_poly_norm(int dtype, const void* z, long n_rows, int width, const void* coef, float eps, void* out, mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    MIXERS_DISPATCH(dtype, poly_norm_kernel<T><<<(int)n_rows, 256, 0, (cudaStream_t)stream>>>((const T*)z, n_rows, width, (const T*)coef, eps, (T*)out));
+    return mixers_status();
+}
+
+extern "C" int mixers_soft_cap(int dtype, const void* x, long n, float cap, float* out, mixers_stream_t stream) {
+    if (n <= 0) return 0;
+    MIXERS_DISPATCH(dtype, soft_cap_kernel<T><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((const T*)x, n, cap, out));
+    return mixers_status();
+}

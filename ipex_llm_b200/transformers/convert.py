@@ -160,6 +160,10 @@ def _optimize_pre(model, qtype=None):
     elif model_type == "mixtral":
         from ipex_llm_b200.transformers.models.mixtral import merge_qkv
         model.apply(merge_qkv)
+    elif model_type == "zafepel":
+        # every projection that reads a mixer's input -> one in_proj; a parallel mixer's two output projections -> one out_proj
+        from ipex_llm_b200.transformers.models.zafepel import merge_projections
+        model.apply(merge_projections)
     return model
 
 
@@ -191,6 +195,9 @@ def _optimize_post(model):
         convert_forward(model, module.MixtralRMSNorm, rms_norm_forward)
         convert_forward(model, module.MixtralModel, mixtral_model_forward)
         convert_forward(model, module.MixtralAttention, mixtral_attention_forward)
+    elif model_type == "zafepel":
+        # this package's own model class: its forwards already call the fused operators and pick the state cache
+        return model
     else:
         return model
     if hasattr(model, "generate"):

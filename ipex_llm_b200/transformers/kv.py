@@ -13,8 +13,9 @@ import os
 import torch
 from transformers.cache_utils import Cache, DynamicLayer
 
-import ipex_llm_b200.ggml.model.llama.llama_cpp as ggml
-from ipex_llm_b200.utils.common import invalidInputError
+from ipex_llm_b200.utils.common import invalidInputError, LazyModule
+
+ggml = LazyModule("ipex_llm_b200.ggml.model.llama.llama_cpp")      # only the FP8 cache and its attention call it
 
 FP8_KV_ALLOC_LENGTH = 512
 KV_ALLOC_BLOCK_LENGTH = int(os.environ.get("KV_CACHE_ALLOC_BLOCK_LENGTH", 256))
@@ -340,3 +341,178 @@ def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: 
         with sdpa_kernel(SDPBackend.MATH):
             return torch.nn.functional.scaled_dot_product_attention(query, key, value, **kwargs)
     return torch.nn.functional.scaled_dot_product_attention(query, key, value, **kwargs)
+
+
+# ------------------------------------------------------------------ caches of models that mix attention with recurrences
+class WindowKVLayer(NormalKVLayer):
+    """Keys and values of an attention layer that looks back ``window`` positions (0 = without limit).  Same block-grown
+    storage as ``NormalKVLayer``; the kernels that fill it (rotary + append in one launch) write into ``slots(n)`` -- the
+    storage with room for ``n`` more positions -- and ``commit(n)`` then moves the length.  Once the layer holds more than
+    ``TRIM_FACTOR`` windows, ``trim`` drops what no later query can see (by then most of the storage) so that a long
+    generation holds O(window) positions; ``dropped`` counts the slots that left, and slot numbers stay absolute."""
+    TRIM_FACTOR = 4
+
+    def __init__(self, reserve: int = 0, window: int = 0):
+        super().__init__(reserve)
+        self.window = int(window)
+        self.dropped = 0
+
+    def slots(self, like_k, like_v, n_new):
+        """(k storage, v storage, positions held) with capacity for n_new more; like_* give [B, G, *, D] shape and dtype"""
+        if not self.is_initialized:
+            self.lazy_initialization(like_k, like_v)
+        cur = 0 if self.keys is None else self.keys.size(2)
+        need = cur + n_new
+        if self.keys is None or self.keys.stride(1) < need * self.keys.size(3):
+            cap = max(need, self.reserve) + KV_ALLOC_BLOCK_LENGTH
+            nk, nv = self._alloc(like_k, cur, cap), self._alloc(like_v, cur, cap)
+            if cur:
+                nk.copy_(self.keys)
+                nv.copy_(self.values)
+            self.keys, self.values = nk, nv
+        return self.keys, self.values, cur
+
+    def commit(self, n_new):
+        for name in ("keys", "values"):
+            t = getattr(self, name)
+            b, h, cur, d = t.shape
+            setattr(self, name, t.as_strided((b, h, cur + n_new, d), t.stride(), storage_offset=0))
+
+    def capacity(self):
+        return 0 if self.keys is None else self.keys.stride(1) // self.keys.size(3)
+
+    def trim(self):
+        if not self.window or self.keys is None or self.keys.size(2) <= self.TRIM_FACTOR * self.window + KV_ALLOC_BLOCK_LENGTH:
+            return
+        keep = self.window - 1
+        cur = self.keys.size(2)
+        for name in ("keys", "values"):
+            t = getattr(self, name)
+            fresh = self._alloc(t, keep, keep + KV_ALLOC_BLOCK_LENGTH + self.window)
+            fresh.copy_(t[:, :, cur - keep:, :])
+            setattr(self, name, fresh)
+        self.dropped += cur - keep
+
+    def select(self, index):
+        if self.keys is not None:
+            for name in ("keys", "values"):
+                t = getattr(self, name)
+                cur = t.size(2)
+                fresh = self._alloc(t.index_select(0, index)[:, :, :0], cur, self.capacity())
+                fresh.copy_(t.index_select(0, index))
+                setattr(self, name, fresh)
+
+
+class RecurrentStateLayer:
+    """What a linear recurrence carries from token to token: the matrix state [B, H, D, Dv] in 32-bit floats and, where a
+    short convolution precedes it, the last ``taps - 1`` inputs of every channel [B, taps - 1, C].  The convolution kernel reads
+    one tail buffer and writes the other (``flip_tail``), so that no thread reads what another has replaced."""
+
+    def __init__(self):
+        self.state = None
+        self.tail = None
+        self.tail_next = None
+
+    def matrix(self, batch, heads, dim, vdim, device):
+        if self.state is None:
+            self.state = torch.zeros(batch, heads, dim, vdim, dtype=torch.float32, device=device)
+        return self.state
+
+    def tails(self, batch, taps, channels, dtype, device):
+        if self.tail is None:
+            self.tail = torch.zeros(batch, max(taps - 1, 1), channels, dtype=dtype, device=device)
+            self.tail_next = torch.empty_like(self.tail)
+        return self.tail, self.tail_next
+
+    def flip_tail(self):
+        self.tail, self.tail_next = self.tail_next, self.tail
+
+    def select(self, index):
+        for name in ("state", "tail", "tail_next"):
+            t = getattr(self, name)
+            if t is not None:
+                setattr(self, name, t.index_select(0, index).contiguous())
+
+
+class MixerStateLayer:
+    """the state of one RUN of a layer (a layer that a model runs several times keeps one of these per run): a window of
+    keys and values, a recurrent state, or both for a layer that runs the two side by side"""
+
+    def __init__(self, window=None, reserve=0):
+        self.kv = WindowKVLayer(reserve, window) if window is not None else None
+        self.rec = RecurrentStateLayer()
+
+    def select(self, index):
+        if self.kv is not None:
+            self.kv.select(index)
+        self.rec.select(index)
+
+
+class DynamicStateCache(Cache):
+    """Cache of a model whose layers are windowed attention, linear recurrences or both.  Rows of a batch advance together:
+    ``seen`` slots have been fed to every row; row b's first ``pad[b]`` slots are left padding (its token in slot c has position
+    c - pad[b]).  ``batch_select_indices`` keeps a subset of the rows (requests that ended leave the batch)."""
+
+    def __init__(self, reserve: int = 0):
+        super().__init__(layers=[])
+        self.reserve = int(reserve)
+        self.seen = 0
+        self.pad = None                                  # int32 [B] on the model's device
+
+    def run_state(self, run_idx, window=None):
+        while len(self.layers) <= run_idx:
+            self.layers.append(None)
+        if self.layers[run_idx] is None:
+            self.layers[run_idx] = MixerStateLayer(window, self.reserve)
+        return self.layers[run_idx]
+
+    def start(self, attention_mask, batch, length, device):
+        """the first call of a batch: left padding from the mask (ones after zeros in every row)"""
+        if attention_mask is None:
+            self.pad = torch.zeros(batch, dtype=torch.int32, device=device)
+        else:
+            m = attention_mask[:, :length].to(device=device, dtype=torch.int32)
+            pad = length - m.sum(dim=1)
+            ok = (m.cumsum(1) == (torch.arange(length, device=device)[None, :] + 1 - pad[:, None]).clamp(min=0)).all()
+            invalidInputError(bool(ok), "attention_mask must be left padding: zeros, then ones, in every row")
+            self.pad = pad.to(torch.int32).contiguous()
+
+    def advance(self, n):
+        self.seen += n
+        for l in self.layers:
+            if l is not None and l.kv is not None:
+                l.kv.trim()
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return self.seen
+
+    def get_mask_sizes(self, cache_position=None, layer_idx: int = 0):
+        n = 0 if cache_position is None else (cache_position if isinstance(cache_position, int) else cache_position.shape[0])
+        return self.seen + n, 0
+
+    def get_max_cache_shape(self, layer_idx: int = 0) -> int:
+        return -1
+
+    @property
+    def is_compileable(self):
+        return False
+
+    def batch_select_indices(self, indices):
+        indices = torch.as_tensor(indices, dtype=torch.int64, device=self.pad.device)
+        self.pad = self.pad.index_select(0, indices).contiguous()
+        for l in self.layers:
+            if l is not None:
+                l.select(indices)
+
+    def reorder_cache(self, beam_idx):
+        self.batch_select_indices(beam_idx)
+
+    def batch_repeat_interleave(self, repeats):
+        n = self.pad.shape[0]
+        self.batch_select_indices(torch.arange(n, device=self.pad.device).repeat_interleave(repeats))
+
+    def crop(self, max_length):
+        invalidInputError(False, "a recurrent state cannot be rolled back to an earlier length")
+
+    def reset(self):
+        self.layers, self.seen, self.pad = [], 0, None

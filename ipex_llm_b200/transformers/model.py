@@ -34,8 +34,42 @@ def save_low_bit(self, save_dir, *args, **kwargs):
         self.to(origin_device)
 
 
+# designs that no library ships: config.json's "architecture" -> the module of this package that defines the model
+# (``load_pretrained(model_dir, torch_dtype)`` builds it from config.json + model.safetensors)
+NATIVE_ARCHITECTURES = {"Zafepel": "ipex_llm_b200.transformers.models.zafepel"}
+
+
+def native_architecture(model_dir):
+    """the defining module's name if ``model_dir``/config.json names one of NATIVE_ARCHITECTURES, else None"""
+    path = os.path.join(str(model_dir), "config.json")
+    if not os.path.isfile(path):
+        return None
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+    except (OSError, ValueError):
+        return None
+    arch = raw.get("architecture")
+    if arch is None and isinstance(raw.get("architectures"), list) and raw["architectures"]:
+        arch = str(raw["architectures"][0]).replace("ForCausalLM", "")
+    return NATIVE_ARCHITECTURES.get(arch)
+
+
 class _BaseAutoModelClass:
     HF_MODEL = None
+
+    @classmethod
+    def _load_base(cls, *args, **kwargs):
+        """the unconverted model: one of this package's own designs by config.json, else Hugging Face's class"""
+        path = args[0] if args else kwargs.get("pretrained_model_name_or_path")
+        native = native_architecture(path) if path is not None else None
+        if native is None:
+            return cls.HF_MODEL.from_pretrained(*args, **kwargs)
+        import importlib
+        from ipex_llm_b200.transformers.convert import _optimize_pre
+        dtype = kwargs.get("torch_dtype", kwargs.get("dtype"))
+        model = importlib.import_module(native).load_pretrained(path, torch_dtype=dtype)
+        return _optimize_pre(model)                      # such a model's forward runs on its merged projections only
 
     @classmethod
     def from_pretrained(cls, *args, **kwargs):
@@ -51,14 +85,14 @@ class _BaseAutoModelClass:
         if load_in_4bit or load_in_low_bit:
             q_k = load_in_low_bit if load_in_low_bit else "sym_int4"
             return cls.load_convert(q_k, optimize_model, modules_to_not_convert, *args, mixed_precision=mixed_precision, **kwargs)
-        return cls.HF_MODEL.from_pretrained(*args, **kwargs)
+        return cls._load_base(*args, **kwargs)
 
     @classmethod
     def load_convert(cls, q_k, optimize_model, modules_to_not_convert, *args, mixed_precision=False, **kwargs):
         """MD:436-530"""
         from ipex_llm_b200.transformers.convert import ggml_convert_low_bit
         invalidInputError(q_k in ggml_tensor_qtype, f"Unknown load_in_low_bit value: {q_k}")
-        model = cls.HF_MODEL.from_pretrained(*args, **kwargs)
+        model = cls._load_base(*args, **kwargs)
         model = model.to("cpu")
         model = ggml_convert_low_bit(model, ggml_tensor_qtype[q_k], optimize_model,
                                      modules_to_not_convert=modules_to_not_convert,

@@ -9,9 +9,9 @@ contiguous); nothing is copied.
 """
 import torch
 
-import ipex_llm_b200.ggml.model.llama.llama_cpp as ggml
-from ipex_llm_b200.utils.common import invalidInputError
-from ipex_llm_b200.transformers.low_bit_linear import _on_device
+from ipex_llm_b200.utils.common import invalidInputError, LazyModule
+
+ggml = LazyModule("ipex_llm_b200.ggml.model.llama.llama_cpp")      # loaded by the first call of one of its kernels
 
 
 def _stream(device):
@@ -102,11 +102,28 @@ def merge_linear(linears: List[torch.nn.Linear]) -> torch.nn.Linear:
     if not hasattr(linears[0], "weight"):
         return None
     new_weight = torch.cat([linear.weight.data for linear in linears], dim=0)
-    has_bias = linears[0].bias is not None
+    has_bias = any(linear.bias is not None for linear in linears)
     with torch.device("meta"):
         new_linear = torch.nn.Linear(1, 1, bias=has_bias)
     if has_bias:
-        new_linear.bias = torch.nn.Parameter(torch.cat([linear.bias.data for linear in linears], dim=0), requires_grad=False)
+        # a part without a bias contributes zeros (the reference only merges parts that agree; a mixer that reads one input
+        # through biased and unbiased projections merges here too)
+        biases = [linear.bias.data if linear.bias is not None
+                  else torch.zeros(linear.weight.shape[0], dtype=linear.weight.dtype, device=linear.weight.device) for linear in linears]
+        new_linear.bias = torch.nn.Parameter(torch.cat(biases, dim=0), requires_grad=False)
+    new_linear.weight = torch.nn.Parameter(new_weight, requires_grad=False)
+    new_linear.in_features = new_weight.size(1)
+    new_linear.out_features = new_weight.size(0)
+    return new_linear
+
+
+def merge_linear_inputs(linears: List[torch.nn.Linear]) -> torch.nn.Linear:
+    """one Linear over the concatenation of the parts' INPUTS: y = sum_i W_i x_i = [W_1 | W_2 | ...] [x_1; x_2; ...], so that the
+    sum of several branches' output projections is taken in the accumulator of one matrix product (bias-free parts)"""
+    invalidInputError(all(linear.bias is None for linear in linears), "merge_linear_inputs takes projections without bias")
+    new_weight = torch.cat([linear.weight.data for linear in linears], dim=1)
+    with torch.device("meta"):
+        new_linear = torch.nn.Linear(1, 1, bias=False)
     new_linear.weight = torch.nn.Parameter(new_weight, requires_grad=False)
     new_linear.in_features = new_weight.size(1)
     new_linear.out_features = new_weight.size(0)
@@ -183,6 +200,7 @@ def rms_norm_forward(self, hidden_states: torch.Tensor):
             x_2d = x_2d.contiguous()
         out_dtype = x_2d.dtype if weight.dtype == x_2d.dtype else torch.promote_types(weight.dtype, x_2d.dtype)
         out = torch.empty(x_2d.shape, dtype=out_dtype, device=x_2d.device)
+        from ipex_llm_b200.transformers.low_bit_linear import _on_device
         with _on_device(x_2d.device):
             ggml.lowbit_rms_norm(x_2d, weight, eps, out, _stream(x_2d.device))
         return out.reshape(hidden_states.shape)

@@ -1,0 +1,131 @@
+"""Host side of the mixer kernels (ggml/model/mixers_cpp.py -> libb200mixers.so): argument checks, output allocation, one
+native call each.  Every function takes CUDA tensors; the shapes are those of include/b200_mixers.h.
+
+Conventions: ``x`` is the 32-bit residual stream [N, W] (N = batch * new tokens); projections are [B, S, P] tensors of the
+model's dtype whose columns hold several quantities side by side (``off_*`` = first column of one); ``slot0`` numbers the
+first new token's slot and ``pad`` [B] int32 is the rows' left padding."""
+import torch
+
+from ipex_llm_b200.ggml.model import mixers_cpp as native
+from ipex_llm_b200.utils.common import invalidInputError
+
+
+def _c(t):
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def embed_rows(table, ids):
+    """fp32 [N, W] rows of the embedding table"""
+    table, ids = _c(table), _c(ids.to(torch.int64))
+    x = torch.empty(ids.numel(), table.shape[1], dtype=torch.float32, device=table.device)
+    native.call("mixers_embed_rows", native.dtype_code(table.dtype), native.ptr(table), native.ptr(ids), ids.numel(), table.shape[1],
+                native.ptr(x), native.stream(x.device))
+    return x
+
+
+def dyt_residual_norm(x, pending, add, pre, out_dtype):
+    """x += DyT_post(y) for ``pending`` = (y, post norm module); x += add; returns DyT_pre(x) in ``out_dtype`` (None without
+    ``pre``).  One launch; x is updated in place."""
+    invalidInputError(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "the residual stream is a contiguous fp32 [N, W]")
+    n, w = x.shape
+    y, post = pending if pending is not None else (None, None)
+    if y is not None:
+        y = _c(y)
+        invalidInputError(y.shape == x.shape and y.dtype == out_dtype, "sublayer output must match the residual's shape and the model's dtype")
+    out = torch.empty(n, w, dtype=out_dtype, device=x.device) if pre is not None else None
+    for mod in (post, pre):
+        if mod is not None:
+            invalidInputError(mod.weight.dtype == out_dtype, "normalisation parameters must have the model's dtype")
+    native.call("mixers_dyt_residual_norm", native.dtype_code(out_dtype), native.ptr(x), n, w, native.ptr(y),
+                native.ptr(post.weight) if post is not None else None, native.ptr(post.bias) if post is not None else None,
+                native.ptr(post.alpha) if post is not None else None, native.ptr(_c(add)) if add is not None else None,
+                native.ptr(pre.weight) if pre is not None else None, native.ptr(pre.bias) if pre is not None else None,
+                native.ptr(pre.alpha) if pre is not None else None, native.ptr(out), native.stream(x.device))
+    return out
+
+
+def window_qk_prepare(proj, off_q, off_k, off_v, heads, kv_heads, dim, vdim, q_w, k_w, eps, inv_freq, rot_dims, k_store, v_store,
+                      cap, held, shift, pad):
+    """norm + rotary of the new tokens' queries and keys, cache write of keys and values; returns q fp32 [B, S, heads, dim]"""
+    B, S, P = proj.shape
+    invalidInputError(proj.is_contiguous() and k_store.stride(-1) == 1 and k_store.stride(1) == cap * dim and v_store.stride(1) == cap * vdim
+                      and k_store.dtype == proj.dtype and v_store.dtype == proj.dtype and inv_freq.dtype == torch.float32,
+                      "window_qk_prepare: unexpected layout")
+    q = torch.empty(B, S, heads, dim, dtype=torch.float32, device=proj.device)
+    native.call("mixers_window_qk_prepare", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, off_q, off_k, off_v, heads, kv_heads,
+                dim, vdim, native.ptr(q_w), native.ptr(k_w), float(eps), native.ptr(inv_freq), rot_dims, native.ptr(q), native.ptr(k_store),
+                native.ptr(v_store), cap, held, shift, native.ptr(pad), native.stream(proj.device))
+    return q
+
+
+def sigmoid_window_attention(q, k_store, v_store, cap, held, shift, pad, window, scale, head_bias, out, out_col, out_scale):
+    """out[:, out_col : out_col + heads * vdim] = out_scale * attention of the new tokens (see the header)"""
+    B, S, heads, dim = q.shape
+    kv_heads, vdim = k_store.shape[1], v_store.shape[3]
+    invalidInputError(out.is_contiguous() and out.shape[0] == B * S and out.dtype == k_store.dtype, "sigmoid_window_attention: unexpected output")
+    native.call("mixers_sigmoid_window_attention", native.dtype_code(out.dtype), native.ptr(q), native.ptr(k_store), native.ptr(v_store), B, S,
+                heads, kv_heads, dim, vdim, cap, held, shift, native.ptr(pad), int(window), float(scale), native.ptr(head_bias), native.ptr(out),
+                out.shape[1], out_col, float(out_scale), native.stream(out.device))
+
+
+def short_conv_silu(proj, off, channels, weight, tail, tail_next, slot0, pad):
+    """silu(short causal convolution) of ``channels`` columns of proj from column ``off``; writes the next tail"""
+    B, S, P = proj.shape
+    taps = weight.shape[1]
+    invalidInputError(proj.is_contiguous() and weight.is_contiguous() and tail.is_contiguous() and tail_next.is_contiguous()
+                      and weight.shape[0] == channels and tail.shape == (B, max(taps - 1, 1), channels), "short_conv_silu: unexpected layout")
+    y = torch.empty(B, S, channels, dtype=proj.dtype, device=proj.device)
+    native.call("mixers_short_conv_silu", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, off, channels, taps, native.ptr(weight),
+                native.ptr(tail), native.ptr(tail_next), slot0, native.ptr(pad), native.ptr(y), native.stream(proj.device))
+    return y
+
+
+def gated_delta_rule(conv, kv_heads, heads, dim, vdim, proj, off_b, off_a, A_log, dt_bias, state, slot0, pad):
+    """the delta-rule recurrence over the new tokens; state fp32 [B, heads, dim, vdim] in place; returns o fp32 [B, S, heads, vdim]"""
+    B, S, C = conv.shape
+    invalidInputError(C == 2 * kv_heads * dim + heads * vdim and conv.is_contiguous() and proj.is_contiguous()
+                      and state.dtype == torch.float32 and state.is_contiguous() and state.shape == (B, heads, dim, vdim),
+                      "gated_delta_rule: unexpected layout")
+    o = torch.empty(B, S, heads, vdim, dtype=torch.float32, device=conv.device)
+    native.call("mixers_gated_delta_rule", native.dtype_code(conv.dtype), native.ptr(conv), B, S, kv_heads, heads, dim, vdim, native.ptr(proj),
+                proj.shape[-1], off_b, off_a, native.ptr(A_log), native.ptr(dt_bias), native.ptr(state), slot0, native.ptr(pad), native.ptr(o),
+                native.stream(conv.device))
+    return o
+
+
+def gated_linear_attention(proj, heads, dim, vdim, z, tau, state, slot0, pad):
+    """gated linear attention over the new tokens (q | k | v in the first columns of proj, decay logits z)"""
+    B, S, P = proj.shape
+    invalidInputError(proj.is_contiguous() and z.is_contiguous() and z.shape == (B, S, heads * dim) and z.dtype == proj.dtype
+                      and state.dtype == torch.float32 and state.is_contiguous() and state.shape == (B, heads, dim, vdim),
+                      "gated_linear_attention: unexpected layout")
+    o = torch.empty(B, S, heads, vdim, dtype=torch.float32, device=proj.device)
+    native.call("mixers_gated_linear_attention", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, heads, dim, vdim, native.ptr(z),
+                float(tau), native.ptr(state), slot0, native.ptr(pad), native.ptr(o), native.stream(proj.device))
+    return o
+
+
+def gated_rms_norm(o, gate, off_g, weight, eps, out, out_col, out_scale):
+    """out[:, out_col:...] = out_scale * rms_norm(o per head) * weight * silu(gate columns from off_g)"""
+    heads, vdim = o.shape[-2], o.shape[-1]
+    n = o.numel() // (heads * vdim)
+    invalidInputError(o.is_contiguous() and o.dtype == torch.float32 and gate.is_contiguous() and out.is_contiguous() and out.shape[0] == n
+                      and gate.dtype == out.dtype, "gated_rms_norm: unexpected layout")
+    native.call("mixers_gated_rms_norm", native.dtype_code(out.dtype), native.ptr(o), n, heads, vdim, native.ptr(gate), gate.shape[-1], off_g,
+                native.ptr(weight), float(eps), native.ptr(out), out.shape[1], out_col, float(out_scale), native.stream(out.device))
+
+
+def poly_norm(z, coef, eps):
+    z = _c(z)
+    out = torch.empty_like(z)
+    native.call("mixers_poly_norm", native.dtype_code(z.dtype), native.ptr(z), z.numel() // z.shape[-1], z.shape[-1], native.ptr(coef),
+                float(eps), native.ptr(out), native.stream(z.device))
+    return out
+
+
+def soft_cap(x, cap):
+    x = _c(x)
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    native.call("mixers_soft_cap", native.dtype_code(x.dtype), native.ptr(x), x.numel(), float(cap) if cap else 0.0, native.ptr(out),
+                native.stream(x.device))
+    return out

@@ -19,3 +19,18 @@ def invalidOperationError(condition, errMsg, fixMsg=None, cause=None):
         if cause:
             raise cause
         raise RuntimeError(errMsg)
+
+
+class LazyModule:
+    """A module that is imported at its first attribute access.  The ctypes bindings load (and need) their shared
+    library when they are imported; a module that merely names one of them -- the cache classes, say, of which only some
+    call that library -- binds it through this and stays importable without it."""
+
+    def __init__(self, name):
+        self.__dict__["_name"], self.__dict__["_mod"] = name, None
+
+    def __getattr__(self, attr):
+        if self.__dict__["_mod"] is None:
+            import importlib
+            self.__dict__["_mod"] = importlib.import_module(self.__dict__["_name"])
+        return getattr(self.__dict__["_mod"], attr)
