@@ -66,6 +66,7 @@ def ptr(t):
     if t is None:
         return None
     invalidInputError(t.device.type == "cuda", "the mixer kernels run on CUDA tensors only (there is no CPU path)")
+    invalidInputError(t.numel() > 0, "an empty tensor has no data pointer to hand to a kernel")
     return t.data_ptr()
 
 

@@ -358,7 +358,8 @@ class WindowKVLayer(NormalKVLayer):
         self.dropped = 0
 
     def slots(self, like_k, like_v, n_new):
-        """(k storage, v storage, positions held) with capacity for n_new more; like_* give [B, G, *, D] shape and dtype"""
+        """(k storage, v storage, positions held): the storages [B, G, capacity, D] with room for n_new more positions behind
+        the ones held; like_* give [B, G, *, D] shape and dtype"""
         if not self.is_initialized:
             self.lazy_initialization(like_k, like_v)
         cur = 0 if self.keys is None else self.keys.size(2)
@@ -370,7 +371,12 @@ class WindowKVLayer(NormalKVLayer):
                 nk.copy_(self.keys)
                 nv.copy_(self.values)
             self.keys, self.values = nk, nv
-        return self.keys, self.values, cur
+        # the whole storage, not the views of the positions held: a view of length 0 has no data pointer
+        return self._whole(self.keys), self._whole(self.values), cur
+
+    def _whole(self, t):
+        b, h, _, d = t.shape
+        return t.as_strided((b, h, t.stride(1) // d, d), t.stride(), storage_offset=0)
 
     def commit(self, n_new):
         for name in ("keys", "values"):

@@ -48,7 +48,8 @@ def window_qk_prepare(proj, off_q, off_k, off_v, heads, kv_heads, dim, vdim, q_w
                       cap, held, shift, pad):
     """norm + rotary of the new tokens' queries and keys, cache write of keys and values; returns q fp32 [B, S, heads, dim]"""
     B, S, P = proj.shape
-    invalidInputError(proj.is_contiguous() and k_store.stride(-1) == 1 and k_store.stride(1) == cap * dim and v_store.stride(1) == cap * vdim
+    invalidInputError(proj.is_contiguous() and k_store.is_contiguous() and v_store.is_contiguous() and k_store.shape[2] == cap
+                      and v_store.shape[2] == cap
                       and k_store.dtype == proj.dtype and v_store.dtype == proj.dtype and inv_freq.dtype == torch.float32,
                       "window_qk_prepare: unexpected layout")
     q = torch.empty(B, S, heads, dim, dtype=torch.float32, device=proj.device)
@@ -62,7 +63,9 @@ def sigmoid_window_attention(q, k_store, v_store, cap, held, shift, pad, window,
     """out[:, out_col : out_col + heads * vdim] = out_scale * attention of the new tokens (see the header)"""
     B, S, heads, dim = q.shape
     kv_heads, vdim = k_store.shape[1], v_store.shape[3]
-    invalidInputError(out.is_contiguous() and out.shape[0] == B * S and out.dtype == k_store.dtype, "sigmoid_window_attention: unexpected output")
+    invalidInputError(out.is_contiguous() and out.shape[0] == B * S and out.dtype == k_store.dtype and k_store.is_contiguous()
+                      and v_store.is_contiguous() and k_store.shape[2] == cap and v_store.shape[2] == cap,
+                      "sigmoid_window_attention: unexpected layout")
     native.call("mixers_sigmoid_window_attention", native.dtype_code(out.dtype), native.ptr(q), native.ptr(k_store), native.ptr(v_store), B, S,
                 heads, kv_heads, dim, vdim, cap, held, shift, native.ptr(pad), int(window), float(scale), native.ptr(head_bias), native.ptr(out),
                 out.shape[1], out_col, float(out_scale), native.stream(out.device))

@@ -102,7 +102,7 @@ class SigmoidWindowAttention(nn.Module):
         ``model.to(dtype)`` must not round it again."""
         t = self._inv_freq.get(device)
         if t is None:
-            freq = [self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)]
+            freq = [self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)] or [0.0]    # never empty
             t = self._inv_freq[device] = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
         return t
 

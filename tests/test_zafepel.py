@@ -137,8 +137,8 @@ def test_state_cache_bookkeeping():
     like = torch.empty(3, 2, 0, 6)
     k, v, held = st.kv.slots(like, like, 5)
     assert held == 0 and st.kv.capacity() >= 5
-    full = k.as_strided((3, 2, st.kv.capacity(), 6), k.stride())
-    full[:, :, :5] = torch.arange(5.0)[None, None, :, None]
+    assert k.shape == (3, 2, st.kv.capacity(), 6) and k.is_contiguous()
+    k[:, :, :5] = torch.arange(5.0)[None, None, :, None]
     st.kv.commit(5)
     cache.advance(5)
     assert cache.get_seq_length() == 5 and st.kv.keys.shape[2] == 5
@@ -150,7 +150,7 @@ def test_state_cache_bookkeeping():
     old_block, kv.KV_ALLOC_BLOCK_LENGTH = kv.KV_ALLOC_BLOCK_LENGTH, 2
     try:
         k, v, held = st.kv.slots(like[:2], like[:2], 20)
-        k.as_strided((2, 2, st.kv.capacity(), 6), k.stride())[:, :, 5:25] = torch.arange(5.0, 25.0)[None, None, :, None]
+        k[:, :, 5:25] = torch.arange(5.0, 25.0)[None, None, :, None]
         st.kv.commit(20)
         cache.advance(20)
         assert st.kv.dropped == 22 and st.kv.keys[1, 1, :, 3].tolist() == [22.0, 23.0, 24.0]
@@ -228,7 +228,7 @@ def _attention_case(mixers, device, dtype, B, S, held, pad, H, G, D, Dv, rot_dim
         q_gain(proj_all)
     qw, kw = (torch.rand(D, generator=g) + 0.5).to(dtype), (torch.rand(D, generator=g) + 0.5).to(dtype)
     hb = (torch.randn(H, generator=g) - 0.5).to(dtype)
-    inv_freq = torch.tensor([50.0 ** (-2.0 * i / rot_dims) for i in range(rot_dims // 2)], dtype=F64).float()
+    inv_freq = torch.tensor([50.0 ** (-2.0 * i / rot_dims) for i in range(rot_dims // 2)] or [0.0], dtype=F64).float()
     pad_t = torch.tensor(pad, dtype=torch.int32)
     oq, ok, ov = 5, 5 + H * D, 5 + H * D + G * D
     scale = 1.3 / math.sqrt(D)
