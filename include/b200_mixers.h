@@ -30,18 +30,19 @@ int mixers_dyt_residual_norm(int dtype, float* x, long n_rows, int width, const 
 /* Queries, keys and values of new tokens taken from the columns of one projection output `proj` [B, S, ld]: per-head RMS norm
  * (weights q_w / k_w [dim]), rotation of the pairs (2i, 2i+1), i < rot_dims / 2, by position * inv_freq[i]; queries go to
  * q_out float [B, S, heads, dim], keys and values into the caches k_store [B, kv_heads, cap, dim] / v_store [.., vdim] at
- * storage index held + t.  The token at storage index j sits in slot j + shift. */
+ * storage index held + t.  The token at storage index j sits in slot j + shift.  dyn (may be null): a device word that holds
+ * `held` instead of the argument, for a step that is replayed from a CUDA graph while the cache grows. */
 int mixers_window_qk_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads,
                              int kv_heads, int dim, int vdim, const void* q_w, const void* k_w, float eps, const float* inv_freq,
                              int rot_dims, float* q_out, void* k_store, void* v_store, int cap, int held, int shift,
-                             const int32_t* pad, mixers_stream_t stream);
+                             const int32_t* pad, const int32_t* dyn, mixers_stream_t stream);
 
 /* out[b, t, out_col + h * vdim + :] = out_scale * sum_j sigmoid(q . k_j * scale + head_bias[h]) v_j over the keys j of the same
  * row with 0 <= c - j < window (c = held + t the query's own storage index) that are not padding.  out: dtype [B * S, ld_out]. */
 int mixers_sigmoid_window_attention(int dtype, const float* q, const void* k_store, const void* v_store, int B, int S, int heads,
                                     int kv_heads, int dim, int vdim, int cap, int held, int shift, const int32_t* pad, int window,
                                     float scale, const void* head_bias, void* out, int ld_out, int out_col, float out_scale,
-                                    mixers_stream_t stream);
+                                    const int32_t* dyn, mixers_stream_t stream);
 
 /* y[b, t, c] = silu(sum_j w[c, j] * in(t - taps + 1 + j)): in(t') = proj[b, t', off + c] for a new token, tail[b, taps-1+t', c]
  * for t' < 0, zero for padding.  tail_next receives the last taps-1 inputs.  w: [C, taps]; tails: [B, max(taps-1,1), C]. */

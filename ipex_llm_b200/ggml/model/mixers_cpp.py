@@ -24,9 +24,9 @@ _SIGNATURES = {
     "mixers_embed_rows": [_c_int, _c_ptr, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr],
     "mixers_dyt_residual_norm": [_c_int, _c_ptr, _c_long, _c_int] + [_c_ptr] * 9 + [_c_ptr],
     "mixers_window_qk_prepare": [_c_int, _c_ptr] + [_c_int] * 10 + [_c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
-                                                                 _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                                                                 _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_sigmoid_window_attention": [_c_int, _c_ptr, _c_ptr, _c_ptr] + [_c_int] * 9 + [_c_ptr, _c_int, _c_float, _c_ptr, _c_ptr, _c_int,
-                                                                                          _c_int, _c_float, _c_ptr],
+                                                                                          _c_int, _c_float, _c_ptr, _c_ptr],
     "mixers_short_conv_silu": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_gated_delta_rule": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
                                                                  _c_ptr, _c_ptr],

@@ -45,21 +45,22 @@ def dyt_residual_norm(x, pending, add, pre, out_dtype):
 
 
 def window_qk_prepare(proj, off_q, off_k, off_v, heads, kv_heads, dim, vdim, q_w, k_w, eps, inv_freq, rot_dims, k_store, v_store,
-                      cap, held, shift, pad):
+                      cap, held, shift, pad, dyn=None, q=None):
     """norm + rotary of the new tokens' queries and keys, cache write of keys and values; returns q fp32 [B, S, heads, dim]"""
     B, S, P = proj.shape
     invalidInputError(proj.is_contiguous() and k_store.is_contiguous() and v_store.is_contiguous() and k_store.shape[2] == cap
                       and v_store.shape[2] == cap
                       and k_store.dtype == proj.dtype and v_store.dtype == proj.dtype and inv_freq.dtype == torch.float32,
                       "window_qk_prepare: unexpected layout")
-    q = torch.empty(B, S, heads, dim, dtype=torch.float32, device=proj.device)
+    if q is None:
+        q = torch.empty(B, S, heads, dim, dtype=torch.float32, device=proj.device)
     native.call("mixers_window_qk_prepare", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, off_q, off_k, off_v, heads, kv_heads,
                 dim, vdim, native.ptr(q_w), native.ptr(k_w), float(eps), native.ptr(inv_freq), rot_dims, native.ptr(q), native.ptr(k_store),
-                native.ptr(v_store), cap, held, shift, native.ptr(pad), native.stream(proj.device))
+                native.ptr(v_store), cap, held, shift, native.ptr(pad), native.ptr(dyn), native.stream(proj.device))
     return q
 
 
-def sigmoid_window_attention(q, k_store, v_store, cap, held, shift, pad, window, scale, head_bias, out, out_col, out_scale):
+def sigmoid_window_attention(q, k_store, v_store, cap, held, shift, pad, window, scale, head_bias, out, out_col, out_scale, dyn=None):
     """out[:, out_col : out_col + heads * vdim] = out_scale * attention of the new tokens (see the header)"""
     B, S, heads, dim = q.shape
     kv_heads, vdim = k_store.shape[1], v_store.shape[3]
@@ -68,7 +69,7 @@ def sigmoid_window_attention(q, k_store, v_store, cap, held, shift, pad, window,
                       "sigmoid_window_attention: unexpected layout")
     native.call("mixers_sigmoid_window_attention", native.dtype_code(out.dtype), native.ptr(q), native.ptr(k_store), native.ptr(v_store), B, S,
                 heads, kv_heads, dim, vdim, cap, held, shift, native.ptr(pad), int(window), float(scale), native.ptr(head_bias), native.ptr(out),
-                out.shape[1], out_col, float(out_scale), native.stream(out.device))
+                out.shape[1], out_col, float(out_scale), native.ptr(dyn), native.stream(out.device))
 
 
 def short_conv_silu(proj, off, channels, weight, tail, tail_next, slot0, pad):

@@ -265,6 +265,20 @@ def test_window_attention_alone(mixers, cuda_device, dtype, tol, S, held):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,Dv,H,G", [(48, 32, 4, 2), (128, 128, 2, 1), (32, 80, 3, 3), (160, 16, 2, 2)])
+@pytest.mark.parametrize("S,held,window", [(70, 50, 40), (130, 0, 300), (16, 3, 7)])
+def test_window_attention_many_tokens_16bit(mixers, cuda_device, dtype, D, Dv, H, G, S, held, window):
+    """the tensor-core path: head sizes that tile into 16s, portions that end inside a 64-row block, windows shorter and longer
+    than a block, padding, a filled cache in front"""
+    got, want = _attention_case(mixers, cuda_device, dtype, B=2, S=S, held=held, pad=[0, 5], H=H, G=G, D=D, Dv=Dv, rot_dims=16,
+                                window=window, seed=D + S)
+    # keys and queries are rounded to 16 bits on the way (2^-9 relative each); the weights keep 16 bits
+    assert (got - want).abs().max() < 2e-2 * max(1.0, want.abs().max())
+    assert (got - want).pow(2).mean().sqrt() < 4e-3 * want.pow(2).mean().sqrt().clamp(min=0.1)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("held,S", [(0, 40), (39, 1)])            # the edge inside a prompt, and met by a decoded token
 def test_window_edge_decides(mixers, cuda_device, held, S):
     """every key but one scores far below zero (weight ~ 0); the one that stands out sits either at distance window - 1
