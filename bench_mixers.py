@@ -33,7 +33,7 @@ def zafepel_config():
 
 def build_zafepel(dev, dtype):
     import torch
-    from ipex_llm_b200.transformers.convert import _optimize_pre
+    from ipex_llm_b200.transformers.convert import _optimize_pre, _optimize_post
     from ipex_llm_b200.transformers.models.zafepel import ZafepelConfig, ZafepelForCausalLM
     cfg = ZafepelConfig(**zafepel_config())
     with torch.device("meta"):
@@ -53,7 +53,7 @@ def build_zafepel(dev, dtype):
             else:
                 t.normal_(0.0, 0.1, generator=gen)
             mod._parameters[name] = torch.nn.Parameter(t.to(dtype), requires_grad=False)
-    return _optimize_pre(model.eval())
+    return _optimize_post(_optimize_pre(model.eval()))
 
 
 def build_llama(dev, dtype):
@@ -103,16 +103,17 @@ class Timer:
 def throughput(model, dev, timer, batch):
     """(prefill tok/s, decode tok/s) through forward / generate() of the public model object"""
     import torch
-    ids = torch.randint(0, VOCAB, (batch, PROMPT), device=dev)
+    ids = torch.randint(1, VOCAB, (batch, PROMPT), device=dev)
+    mask = torch.ones_like(ids)
     with torch.no_grad():
         ms_prefill = timer(lambda: model(input_ids=ids, use_cache=True, logits_to_keep=1), runs=5, warmup=2)
         torch.cuda.synchronize()
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        model.generate(input_ids=ids, max_new_tokens=4, do_sample=False, pad_token_id=0)          # warm-up (records graphs)
+        model.generate(input_ids=ids, attention_mask=mask, max_new_tokens=4, do_sample=False, pad_token_id=0)          # warm-up (records graphs)
         ev[0].record()
-        model.generate(input_ids=ids, max_new_tokens=1, do_sample=False, pad_token_id=0)
+        model.generate(input_ids=ids, attention_mask=mask, max_new_tokens=1, do_sample=False, pad_token_id=0)
         ev[1].record()
-        model.generate(input_ids=ids, max_new_tokens=1 + NEW, do_sample=False, pad_token_id=0)
+        model.generate(input_ids=ids, attention_mask=mask, max_new_tokens=1 + NEW, do_sample=False, pad_token_id=0)
         ev[2].record()
         torch.cuda.synchronize()
     ms_decode = (ev[1].elapsed_time(ev[2]) - ev[0].elapsed_time(ev[1])) / NEW

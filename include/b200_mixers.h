@@ -45,7 +45,9 @@ int mixers_sigmoid_window_attention(int dtype, const float* q, const void* k_sto
                                     const int32_t* dyn, mixers_stream_t stream);
 
 /* y[b, t, c] = silu(sum_j w[c, j] * in(t - taps + 1 + j)): in(t') = proj[b, t', off + c] for a new token, tail[b, taps-1+t', c]
- * for t' < 0, zero for padding.  tail_next receives the last taps-1 inputs.  w: [C, taps]; tails: [B, max(taps-1,1), C]. */
+ * for t' < 0, zero for padding.  tail_next receives the last taps-1 inputs (for S == 1 it may be `tail` itself: a thread
+ * then owns its channel's whole tail).  w: [C, taps]; tails: [B, max(taps-1,1), C].  In this and the two recurrences `pad` may
+ * be null: none of the new tokens is padding (true for every call but a batch's first). */
 int mixers_short_conv_silu(int dtype, const void* proj, int B, int S, int ld, int off, int C, int taps, const void* w,
                            const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream);
 

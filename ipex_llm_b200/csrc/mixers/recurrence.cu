@@ -21,7 +21,7 @@ __global__ void short_conv_silu_kernel(const T* __restrict__ proj, int B, int S,
         int c = (int)(i % C);
         long n = i / C;
         int b = (int)(n / S), t = (int)(n - (long)b * S);
-        int first = pad[b] - slot0;                          // new tokens before this index are padding
+        int first = pad ? pad[b] - slot0 : 0;                // new tokens before this index are padding
         if (first < 0) first = 0;
         auto input = [&](int tt) -> float {
             if (tt < 0) return to_f(tail[((long)b * tl + (taps - 1 + tt)) * C + c]);
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs 
         int i = r * lpc + sub;
         M[r] = (col_ok && i < dim) ? st[(long)i * vdim + col] : 0.0f;
     }
-    int first = a.pad[b] - a.slot0;
+    int first = a.pad ? a.pad[b] - a.slot0 : 0;
     if (first < 0) first = 0;
     if (first > S) first = S;
     float* obase = a.o + (((long)b * S) * a.heads + h) * vdim;

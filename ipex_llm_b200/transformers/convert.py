@@ -196,8 +196,10 @@ def _optimize_post(model):
         convert_forward(model, module.MixtralModel, mixtral_model_forward)
         convert_forward(model, module.MixtralAttention, mixtral_attention_forward)
     elif model_type == "zafepel":
-        # this package's own model class: its forwards already call the fused operators and pick the state cache
-        return model
+        # this package's own model class: its forwards already call the fused operators and pick the state cache;
+        # the recorded decode step for such a cache goes behind generate()
+        from ipex_llm_b200.transformers.state_decode_graph import install_state_generate
+        return install_state_generate(model)
     else:
         return model
     if hasattr(model, "generate"):

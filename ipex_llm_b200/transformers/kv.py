@@ -356,6 +356,7 @@ class WindowKVLayer(NormalKVLayer):
         super().__init__(reserve)
         self.window = int(window)
         self.dropped = 0
+        self.length_dev = None            # int32 [1] on the device: the positions held, for a step replayed from a CUDA graph
 
     def slots(self, like_k, like_v, n_new):
         """(k storage, v storage, positions held): the storages [B, G, capacity, D] with room for n_new more positions behind
@@ -386,6 +387,12 @@ class WindowKVLayer(NormalKVLayer):
 
     def capacity(self):
         return 0 if self.keys is None else self.keys.stride(1) // self.keys.size(3)
+
+    def clear(self):
+        """forget the positions held, keep the storage (and its address)"""
+        if self.keys is not None:
+            self.keys, self.values = self._whole(self.keys)[:, :, :0], self._whole(self.values)[:, :, :0]
+        self.dropped = 0
 
     def trim(self):
         if not self.window or self.keys is None or self.keys.size(2) <= self.TRIM_FACTOR * self.window + KV_ALLOC_BLOCK_LENGTH:
@@ -433,6 +440,11 @@ class RecurrentStateLayer:
     def flip_tail(self):
         self.tail, self.tail_next = self.tail_next, self.tail
 
+    def clear(self):
+        for t in (self.state, self.tail, self.tail_next):
+            if t is not None:
+                t.zero_()
+
     def select(self, index):
         for name in ("state", "tail", "tail_next"):
             t = getattr(self, name)
@@ -453,6 +465,11 @@ class MixerStateLayer:
             self.kv.select(index)
         self.rec.select(index)
 
+    def clear(self):
+        if self.kv is not None:
+            self.kv.clear()
+        self.rec.clear()
+
 
 class DynamicStateCache(Cache):
     """Cache of a model whose layers are windowed attention, linear recurrences or both.  Rows of a batch advance together:
@@ -464,6 +481,7 @@ class DynamicStateCache(Cache):
         self.reserve = int(reserve)
         self.seen = 0
         self.pad = None                                  # int32 [B] on the model's device
+        self.frozen = False                              # storage stays where it is: no trimming (a recorded step holds its addresses)
 
     def run_state(self, run_idx, window=None):
         while len(self.layers) <= run_idx:
@@ -475,19 +493,32 @@ class DynamicStateCache(Cache):
     def start(self, attention_mask, batch, length, device):
         """the first call of a batch: left padding from the mask (ones after zeros in every row)"""
         if attention_mask is None:
-            self.pad = torch.zeros(batch, dtype=torch.int32, device=device)
+            pad = torch.zeros(batch, dtype=torch.int32, device=device)
         else:
             m = attention_mask[:, :length].to(device=device, dtype=torch.int32)
             pad = length - m.sum(dim=1)
             ok = (m.cumsum(1) == (torch.arange(length, device=device)[None, :] + 1 - pad[:, None]).clamp(min=0)).all()
             invalidInputError(bool(ok), "attention_mask must be left padding: zeros, then ones, in every row")
-            self.pad = pad.to(torch.int32).contiguous()
+            pad = pad.to(torch.int32).contiguous()
+        if self.frozen and self.pad is not None and self.pad.shape == pad.shape:
+            self.pad.copy_(pad)
+        else:
+            self.pad = pad
 
     def advance(self, n):
         self.seen += n
+        if self.frozen:
+            return
         for l in self.layers:
             if l is not None and l.kv is not None:
                 l.kv.trim()
+
+    def restart(self):
+        """forget every token, keep every tensor where it is (the next batch of a recorded step)"""
+        self.seen = 0
+        for l in self.layers:
+            if l is not None:
+                l.clear()
 
     def get_seq_length(self, layer_idx: int = 0) -> int:
         return self.seen

@@ -66,10 +66,11 @@ class _BaseAutoModelClass:
         if native is None:
             return cls.HF_MODEL.from_pretrained(*args, **kwargs)
         import importlib
-        from ipex_llm_b200.transformers.convert import _optimize_pre
+        from ipex_llm_b200.transformers.convert import _optimize_pre, _optimize_post
         dtype = kwargs.get("torch_dtype", kwargs.get("dtype"))
         model = importlib.import_module(native).load_pretrained(path, torch_dtype=dtype)
-        return _optimize_pre(model)                      # such a model's forward runs on its merged projections only
+        # such a model's forward runs on its merged projections only; the recorded decode step goes behind generate()
+        return _optimize_post(_optimize_pre(model))
 
     @classmethod
     def from_pretrained(cls, *args, **kwargs):

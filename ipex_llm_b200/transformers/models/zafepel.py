@@ -241,11 +241,13 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
         like_v = torch.empty((B, l.kv_heads, 0, l.vdim), dtype=h.dtype, device=h.device)
         k_store, v_store, held = kv.slots(like_k, like_v, S)
         shift = cache.seen - held                                            # storage index + shift = slot number
+        # a recorded decode step reads the length from the device (the value given here is the one at recording time)
+        dyn = kv.length_dev if (cache.frozen and S == 1) else None
         q = ops.window_qk_prepare(proj, 0, off_k, off_v, l.heads, l.kv_heads, l.dim, l.vdim, l.q_norm.weight, l.k_norm.weight,
-                                  eps, l.inv_freq(h.device), l.rot_dims, k_store, v_store, kv.capacity(), held, shift, cache.pad)
+                                  eps, l.inv_freq(h.device), l.rot_dims, k_store, v_store, kv.capacity(), held, shift, cache.pad, dyn)
         kv.commit(S)
         ops.sigmoid_window_attention(q, k_store, v_store, kv.capacity(), held, shift, cache.pad, l.window, l.scale, l.pos_bias,
-                                     out, 0, mx.left_scale)
+                                     out, 0, mx.left_scale, dyn)
         # right: q | k | v (convolved) | beta | decay | gate
         qk = r.kv_heads * r.dim
         C = 2 * qk + r.heads * r.vdim
@@ -253,11 +255,15 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
         off_a = off_b + r.heads
         off_g = off_a + r.heads
         tail, tail_next = st.rec.tails(B, r.taps, C, h.dtype, h.device)
-        conv = ops.short_conv_silu(proj, off_r, C, r.conv_weight, tail, tail_next, cache.seen, cache.pad)
-        st.rec.flip_tail()
+        pad = cache.pad if cache.seen == 0 else None                         # padding only ever precedes a row's first call
+        if S == 1:                                                           # one thread per channel: the tail is shifted in place
+            conv = ops.short_conv_silu(proj, off_r, C, r.conv_weight, tail, tail, cache.seen, pad)
+        else:
+            conv = ops.short_conv_silu(proj, off_r, C, r.conv_weight, tail, tail_next, cache.seen, pad)
+            st.rec.flip_tail()
         state = st.rec.matrix(B, r.heads, r.dim, r.vdim, h.device)
         o = ops.gated_delta_rule(conv, r.kv_heads, r.heads, r.dim, r.vdim, proj, off_b, off_a, r.A_log, r.dt_bias, state,
-                                 cache.seen, cache.pad)
+                                 cache.seen, pad)
         ops.gated_rms_norm(o, proj, off_g, r.norm.weight, eps, out, l.out_width(), mx.right_scale)
         return _lin(mx.out_proj, out)
 
@@ -271,7 +277,7 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
         z = _lin(mx.a2_proj, proj[:, off_a1:])                               # [N, H * D] decay logits
         state = st.rec.matrix(B, mx.heads, mx.dim, mx.vdim, h.device)
         o = ops.gated_linear_attention(proj.view(B, S, P), mx.heads, mx.dim, mx.vdim, z.view(B, S, qk), mx.tau, state,
-                                       cache.seen, cache.pad)
+                                       cache.seen, cache.pad if cache.seen == 0 else None)
         out = torch.empty(B * S, v, dtype=h.dtype, device=h.device)
         ops.gated_rms_norm(o, proj.view(B, S, P), off_g, mx.norm.weight, self.config.norm_eps, out, 0, 1.0)
         return _lin(mx.o_proj, out)
@@ -291,7 +297,7 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
         if not isinstance(cache, DynamicStateCache):
             invalidInputError(cache is None or cache.get_seq_length() == 0, "a filled cache of another class cannot be continued")
             cache = DynamicStateCache()
-        if cache.pad is None:
+        if cache.seen == 0:                                                  # a batch's first call: the mask gives the padding
             cache.start(attention_mask, B, S, dev)
         invalidInputError(cache.pad.shape[0] == B, "batch size differs from the cache's")
         x = ops.embed_rows(core.embed_tokens.weight, input_ids.reshape(-1))  # fp32 [N, W]

@@ -562,6 +562,12 @@ def test_greedy_generate_matches_the_oracle(models, cuda_device):
         ids[i, width - len(p):] = torch.tensor(p)
         mask[i, width - len(p):] = 1
     out = model.generate(input_ids=ids.to(cuda_device), attention_mask=mask.to(cuda_device), max_new_tokens=new, do_sample=False, pad_token_id=0)
+    # the recorded step (behind generate) and transformers' own loop on the same forward pick the same tokens
+    slow = model._hf_generate(input_ids=ids.to(cuda_device), attention_mask=mask.to(cuda_device), max_new_tokens=new, do_sample=False,
+                              pad_token_id=0)
+    assert torch.equal(out, slow)
+    again = model.generate(input_ids=ids.to(cuda_device), attention_mask=mask.to(cuda_device), max_new_tokens=new, do_sample=False, pad_token_id=0)
+    assert torch.equal(out, again)                                 # the step's own cache starts clean every time
     om = O.OracleModel(cfg, w)
     for i, p in enumerate(prompts):
         st = om.new_state()
