@@ -31,7 +31,7 @@ def zafepel_config():
             "norm": {"eps": 1e-5}, "vocab": VOCAB, "width": WIDTH}
 
 
-def build_zafepel(dev, dtype):
+def build_zafepel(dev, dtype, low_bit=None):
     import torch
     from ipex_llm_b200.transformers.convert import _optimize_pre, _optimize_post
     from ipex_llm_b200.transformers.models.zafepel import ZafepelConfig, ZafepelForCausalLM
@@ -53,6 +53,9 @@ def build_zafepel(dev, dtype):
             else:
                 t.normal_(0.0, 0.1, generator=gen)
             mod._parameters[name] = torch.nn.Parameter(t.to(dtype), requires_grad=False)
+    if low_bit:                                              # the projections become LowBitLinear like any other model's
+        from ipex_llm.transformers import AutoModelForCausalLM
+        return AutoModelForCausalLM.from_model(model.eval(), low_bit=low_bit).to(dev)
     return _optimize_post(_optimize_pre(model.eval()))
 
 
@@ -237,6 +240,10 @@ def run(args):
     del model
     torch.cuda.empty_cache()
     if not args.no_compare:
+        model = build_zafepel(dev, dtype, low_bit="sym_int4")
+        out["zafepel_sym_int4"] = [throughput(model, dev, timer, b) for b in (1, 8)]
+        del model
+        torch.cuda.empty_cache()
         model = build_llama(dev, torch.float16)
         out["llama_equal_size"] = [throughput(model, dev, timer, b) for b in (1, 8)]
         out["llama_equal_size_note"] = "sym_int4 weights, FP8 KV cache, fp16 activations, same width / ff / heads / layer runs"

@@ -4,8 +4,9 @@
 //   gated delta rule:        M <- g M;  u = beta (v - M^T k);  M <- M + k u^T;  o = M^T q
 //   gated linear attention:  M <- diag(alpha) M + k v^T;       o = M^T q
 // column j only needs k, q, the token's scalars and v_j.  So a column is owned by LPC lanes of a warp (LPC a power of two), each
-// holding R rows of it in registers for the whole call; tokens are taken in order, their k / q (/ alpha) rows, scalars and
-// v staged TC tokens at a time in shared memory by the whole block, unit norms and gates evaluated there in 32-bit floats.
+// holding R rows of it in registers for the whole call; tokens are taken in order.  Half of the block's warps own columns; the
+// other half stage the NEXT 16 tokens meanwhile in the second of two shared-memory buffers: their k / q (/ alpha) rows, scalars
+// and v, with unit norms, decays and gates evaluated there in 32-bit floats.
 // For the delta rule both dot products are taken on the state BEFORE the token's update,
 //   a = M_old^T k,  c = M_old^T q:   u = beta (v - g a),   o = g c + (k . q) u,   M <- g M_old + k u^T,
 // which is the same arithmetic reordered so that one round of shuffles serves both.
@@ -36,8 +37,11 @@ __global__ void short_conv_silu_kernel(const T* __restrict__ proj, int B, int S,
     }
 }
 
-constexpr int REC_THREADS = 128;
-constexpr int REC_TC = 16;                                  // tokens staged at a time (fewer for very wide heads)
+constexpr int REC_CONSUMERS = 128;                          // threads that own state columns (4 warps)
+constexpr int REC_PRODUCERS = 128;                          // threads that stage the next tokens meanwhile (4 warps)
+constexpr int REC_THREADS = REC_CONSUMERS + REC_PRODUCERS;
+constexpr int REC_TPW = 4;                                  // tokens a producer warp stages at a time
+constexpr int REC_TC = REC_TPW * (REC_PRODUCERS / 32);      // tokens per stage (16)
 
 struct RecArgs {
     const void* src;        // delta: conv output [B, S, C]; gla: projection [B, S, ld]
@@ -57,32 +61,109 @@ struct RecArgs {
     int lpc, tc;
 };
 
+// shared memory of one stage: k, q (and alpha) rows of tc tokens padded to dp, the block's value columns, three scalars a token
+template <int MODE>
+struct RecStage {
+    float *k, *q, *a, *v, *sc;
+    __device__ RecStage(float* base, int tc, int dp, int cols_blk) {
+        k = base; q = k + tc * dp; a = q + tc * dp; v = a + (MODE == 1 ? tc * dp : 0); sc = v + tc * cols_blk;
+    }
+    static __host__ __device__ size_t floats(int tc, int dp, int cols_blk) { return (size_t)tc * ((MODE == 1 ? 3 : 2) * dp + cols_blk + 4); }
+};
+
+// producers: tokens t0 .. t0 + nt - 1 of the call into one stage.  A warp takes up to REC_TPW tokens at once so that their loads
+// are in flight together and their reductions overlap.
+template <typename T, int MODE>
+__device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE> st, int b, int h, int qh, int t0, int nt, int dp, int cols_blk,
+                                                 int col0, int ptid) {
+    const int lane = ptid & 31, pw = ptid >> 5;
+    const int dim = a.dim, S = a.S;
+    const T* src = (const T*)a.src;
+    const float q_scale = rsqrtf((float)dim);
+    const int tt0 = pw * REC_TPW;
+    int cnt = nt - tt0;
+    if (cnt > REC_TPW) cnt = REC_TPW;
+    if (cnt > 0) {
+        float sq[REC_TPW], sk[REC_TPW], skq[REC_TPW];
+#pragma unroll
+        for (int j = 0; j < REC_TPW; ++j) sq[j] = sk[j] = skq[j] = 0.0f;
+        for (int i = lane; i < dp; i += 32) {
+            float qv[REC_TPW], kv[REC_TPW];
+#pragma unroll
+            for (int j = 0; j < REC_TPW; ++j) {
+                qv[j] = kv[j] = 0.0f;
+                if (j < cnt && i < dim) {
+                    const T* row = src + ((long)b * S + t0 + tt0 + j) * a.ld_src;
+                    qv[j] = to_f(row[a.off_q + qh * dim + i]);
+                    kv[j] = to_f(row[a.off_k + qh * dim + i]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < REC_TPW; ++j) {
+                if (j < cnt) {
+                    if (MODE == 1) {
+                        const T* zr = (const T*)a.z + ((long)b * S + t0 + tt0 + j) * ((long)a.heads * dim) + h * dim;
+                        st.a[(tt0 + j) * dp + i] = i < dim ? expf(log_sigmoid_f(to_f(zr[i])) * a.inv_tau) : 1.0f;
+                        st.q[(tt0 + j) * dp + i] = qv[j] * q_scale;
+                    } else {
+                        st.q[(tt0 + j) * dp + i] = qv[j];
+                    }
+                    st.k[(tt0 + j) * dp + i] = kv[j];
+                    sq[j] += qv[j] * qv[j]; sk[j] += kv[j] * kv[j]; skq[j] += qv[j] * kv[j];
+                }
+            }
+        }
+        if (MODE == 0) {
+#pragma unroll
+            for (int j = 0; j < REC_TPW; ++j) { sq[j] = warp_sum(sq[j]); sk[j] = warp_sum(sk[j]); skq[j] = warp_sum(skq[j]); }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < REC_TPW; ++j) {
+                if (j < cnt) {
+                    const float nq = q_scale / sqrtf(sq[j] + 1e-6f), nk = 1.0f / sqrtf(sk[j] + 1e-6f);
+                    for (int i = lane; i < dp; i += 32) { st.q[(tt0 + j) * dp + i] *= nq; st.k[(tt0 + j) * dp + i] *= nk; }
+                    if (lane == 0) {
+                        const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt0 + j) * a.ld_proj;
+                        float beta = sigmoid_f(to_f(pr[a.off_b + h]));
+                        float dt = softplus_f(to_f(pr[a.off_a + h]) + to_f(((const T*)a.dt_bias)[h]));
+                        st.sc[(tt0 + j) * 4 + 0] = expf(-expf(to_f(((const T*)a.A_log)[h])) * dt);
+                        st.sc[(tt0 + j) * 4 + 1] = beta;
+                        st.sc[(tt0 + j) * 4 + 2] = skq[j] * nq * nk;
+                    }
+                }
+            }
+        }
+    }
+    for (int i = ptid; i < nt * cols_blk; i += REC_PRODUCERS) {
+        int tt = i / cols_blk, cl = i - tt * cols_blk;
+        int cg = col0 + cl;
+        st.v[i] = cg < a.vdim ? to_f(src[((long)b * S + t0 + tt) * a.ld_src + a.off_v + h * a.vdim + cg]) : 0.0f;
+    }
+}
+
 template <typename T, int MODE, int R>                     // MODE 0: gated delta rule, 1: gated linear attention
 __global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sh[];
     const int lpc = a.lpc, dp = R * lpc, tc = a.tc;
-    const int cols_blk = REC_THREADS / lpc;
-    float* kbuf = sh;                                        // [tc][dp]
-    float* qbuf = kbuf + tc * dp;                            // [tc][dp]
-    float* abuf = qbuf + tc * dp;                            // [tc][dp] (gla only)
-    float* vbuf = abuf + (MODE == 1 ? tc * dp : 0);          // [tc][cols_blk]
-    float* sc = vbuf + tc * cols_blk;                        // [tc][4]: g, beta, k.q
+    const int cols_blk = REC_CONSUMERS / lpc;
+    const size_t stage_floats = RecStage<MODE>::floats(tc, dp, cols_blk);
     const int b = blockIdx.z, h = blockIdx.y;
-    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int sub = tid % lpc;
+    const int tid = threadIdx.x;
+    const bool producer = tid >= REC_CONSUMERS;
+    const int sub = tid % lpc;                               // consumers only
     const int col_l = tid / lpc;
-    const int col = blockIdx.x * cols_blk + col_l;
-    const bool col_ok = col < a.vdim;
+    const int col0 = blockIdx.x * cols_blk;
+    const int col = col0 + col_l;
+    const bool col_ok = !producer && col < a.vdim;
     const int dim = a.dim, vdim = a.vdim, S = a.S;
     const int qh = h / (a.heads / a.q_heads);
-    const T* src = (const T*)a.src;
 
     float M[R];
-    float* st = a.state + ((long)b * a.heads + h) * dim * vdim;
+    float* stp = a.state + ((long)b * a.heads + h) * dim * vdim;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         int i = r * lpc + sub;
-        M[r] = (col_ok && i < dim) ? st[(long)i * vdim + col] : 0.0f;
+        M[r] = (col_ok && i < dim) ? stp[(long)i * vdim + col] : 0.0f;
     }
     int first = a.pad ? a.pad[b] - a.slot0 : 0;
     if (first < 0) first = 0;
@@ -90,81 +171,64 @@ __global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs 
     float* obase = a.o + (((long)b * S) * a.heads + h) * vdim;
     if (sub == 0 && col_ok)
         for (int t = 0; t < first; ++t) obase[(long)t * a.heads * vdim + col] = 0.0f;
-    const float q_scale = rsqrtf((float)dim);
 
-    for (int t0 = first; t0 < S; t0 += tc) {
-        const int nt = S - t0 < tc ? S - t0 : tc;
-        __syncthreads();
-        // ---- stage nt tokens: a warp per token
-        for (int tt = wid; tt < nt; tt += REC_THREADS / 32) {
-            const T* row = src + ((long)b * S + t0 + tt) * a.ld_src;
-            const T* qr = row + a.off_q + qh * dim;
-            const T* kr = row + a.off_k + qh * dim;
-            float sq = 0.0f, sk = 0.0f, skq = 0.0f;
-            for (int i = lane; i < dp; i += 32) {
-                float qv = i < dim ? to_f(qr[i]) : 0.0f, kv = i < dim ? to_f(kr[i]) : 0.0f;
-                qbuf[tt * dp + i] = qv;
-                kbuf[tt * dp + i] = kv;
-                sq += qv * qv; sk += kv * kv; skq += qv * kv;
+    const int nchunks = (S - first + tc - 1) / tc;
+    if (producer && nchunks > 0)
+        rec_stage_tokens<T, MODE>(a, RecStage<MODE>(sh, tc, dp, cols_blk), b, h, qh, first, (S - first < tc ? S - first : tc), dp, cols_blk, col0,
+                                  tid - REC_CONSUMERS);
+    __syncthreads();
+    for (int ci = 0; ci < nchunks; ++ci) {
+        const int t0 = first + ci * tc;
+        if (producer) {
+            if (ci + 1 < nchunks) {
+                const int t1 = t0 + tc;
+                rec_stage_tokens<T, MODE>(a, RecStage<MODE>(sh + ((ci + 1) & 1) * stage_floats, tc, dp, cols_blk), b, h, qh, t1,
+                                          (S - t1 < tc ? S - t1 : tc), dp, cols_blk, col0, tid - REC_CONSUMERS);
             }
-            if (MODE == 0) {
-                sq = warp_sum(sq); sk = warp_sum(sk); skq = warp_sum(skq);
-                const float nq = q_scale / sqrtf(sq + 1e-6f), nk = 1.0f / sqrtf(sk + 1e-6f);
-                __syncwarp();
-                for (int i = lane; i < dp; i += 32) { qbuf[tt * dp + i] *= nq; kbuf[tt * dp + i] *= nk; }
-                if (lane == 0) {
-                    const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt) * a.ld_proj;
-                    float beta = sigmoid_f(to_f(pr[a.off_b + h]));
-                    float dt = softplus_f(to_f(pr[a.off_a + h]) + to_f(((const T*)a.dt_bias)[h]));
-                    sc[tt * 4 + 0] = expf(-expf(to_f(((const T*)a.A_log)[h])) * dt);
-                    sc[tt * 4 + 1] = beta;
-                    sc[tt * 4 + 2] = skq * nq * nk;
+        } else {
+            // the tokens in order; a column's lanes only talk to each other.  Four partial sums per dot product keep the
+            // dependent chains short.
+            const RecStage<MODE> st(sh + (ci & 1) * stage_floats, tc, dp, cols_blk);
+            const int nt = S - t0 < tc ? S - t0 : tc;
+            for (int tt = 0; tt < nt; ++tt) {
+                const float* kk = st.k + tt * dp + sub;
+                const float* qq = st.q + tt * dp + sub;
+                const float v = st.v[tt * cols_blk + col_l];
+                float kr[R], qr[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) { kr[r] = kk[r * lpc]; qr[r] = qq[r * lpc]; }
+                float o;
+                if (MODE == 0) {
+                    const float g = st.sc[tt * 4 + 0], beta = st.sc[tt * 4 + 1], kq = st.sc[tt * 4 + 2];
+                    float ak[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int r = 0; r < R; ++r) { ak[r & 3] += M[r] * kr[r]; cq[r & 3] += M[r] * qr[r]; }
+                    float aks = (ak[0] + ak[1]) + (ak[2] + ak[3]), cqs = (cq[0] + cq[1]) + (cq[2] + cq[3]);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) M[r] *= g;                   // overlaps the shuffles below
+                    for (int m = lpc >> 1; m > 0; m >>= 1) { aks += __shfl_xor_sync(0xffffffffu, aks, m); cqs += __shfl_xor_sync(0xffffffffu, cqs, m); }
+                    const float u = beta * (v - g * aks);
+                    o = g * cqs + kq * u;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) M[r] += kr[r] * u;
+                } else {
+                    const float* aa = st.a + tt * dp + sub;
+                    float op[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int r = 0; r < R; ++r) { M[r] = aa[r * lpc] * M[r] + kr[r] * v; op[r & 3] += M[r] * qr[r]; }
+                    o = (op[0] + op[1]) + (op[2] + op[3]);
+                    for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
                 }
-            } else {
-                const T* zr = (const T*)a.z + ((long)b * S + t0 + tt) * ((long)a.heads * dim) + h * dim;
-                for (int i = lane; i < dp; i += 32) {
-                    qbuf[tt * dp + i] *= q_scale;
-                    abuf[tt * dp + i] = i < dim ? expf(log_sigmoid_f(to_f(zr[i])) * a.inv_tau) : 1.0f;
-                }
+                if (sub == 0 && col_ok) obase[(long)(t0 + tt) * a.heads * vdim + col] = o;
             }
-        }
-        for (int i = tid; i < nt * cols_blk; i += REC_THREADS) {
-            int tt = i / cols_blk, cl = i - tt * cols_blk;
-            int cg = blockIdx.x * cols_blk + cl;
-            vbuf[i] = cg < vdim ? to_f(src[((long)b * S + t0 + tt) * a.ld_src + a.off_v + h * vdim + cg]) : 0.0f;
         }
         __syncthreads();
-        // ---- the tokens in order; a column's lanes only talk to each other
-        for (int tt = 0; tt < nt; ++tt) {
-            const float* kk = kbuf + tt * dp + sub;
-            const float* qq = qbuf + tt * dp + sub;
-            const float v = vbuf[tt * cols_blk + col_l];
-            float o;
-            if (MODE == 0) {
-                float ak = 0.0f, cq = 0.0f;
-#pragma unroll
-                for (int r = 0; r < R; ++r) { ak += M[r] * kk[r * lpc]; cq += M[r] * qq[r * lpc]; }
-                for (int m = lpc >> 1; m > 0; m >>= 1) { ak += __shfl_xor_sync(0xffffffffu, ak, m); cq += __shfl_xor_sync(0xffffffffu, cq, m); }
-                const float g = sc[tt * 4 + 0], beta = sc[tt * 4 + 1], kq = sc[tt * 4 + 2];
-                const float u = beta * (v - g * ak);
-                o = g * cq + kq * u;
-#pragma unroll
-                for (int r = 0; r < R; ++r) M[r] = g * M[r] + kk[r * lpc] * u;
-            } else {
-                const float* aa = abuf + tt * dp + sub;
-                o = 0.0f;
-#pragma unroll
-                for (int r = 0; r < R; ++r) { M[r] = aa[r * lpc] * M[r] + kk[r * lpc] * v; o += M[r] * qq[r * lpc]; }
-                for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-            }
-            if (sub == 0 && col_ok) obase[(long)(t0 + tt) * a.heads * vdim + col] = o;
-        }
     }
     if (col_ok) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             int i = r * lpc + sub;
-            if (i < dim) st[(long)i * vdim + col] = M[r];
+            if (i < dim) stp[(long)i * vdim + col] = M[r];
         }
     }
 }
@@ -176,16 +240,20 @@ static int launch_recurrence(RecArgs a, cudaStream_t stream) {
     int lpc = 1;
     while (lpc < need) lpc <<= 1;
     if (lpc > 32) return (int)cudaErrorInvalidValue;         // heads wider than 1024 rows are not served
-    int dp = r * lpc, cols_blk = REC_THREADS / lpc;
-    int arrays = MODE == 1 ? 3 : 2;
-    int tc = REC_TC;
-    auto bytes = [&](int n) { return (size_t)n * (arrays * dp + cols_blk + 4) * sizeof(float); };
-    while (tc > 1 && bytes(tc) > 40 * 1024) tc >>= 1;
-    if (bytes(tc) > 48 * 1024) return (int)cudaErrorInvalidValue;
-    a.lpc = lpc; a.tc = tc;
+    int dp = r * lpc, cols_blk = REC_CONSUMERS / lpc;
+    size_t bytes = 2 * RecStage<MODE>::floats(REC_TC, dp, cols_blk) * sizeof(float);      // two stages
+    if (bytes > 200 * 1024) return (int)cudaErrorInvalidValue;
+    a.lpc = lpc; a.tc = REC_TC;
     dim3 grid((a.vdim + cols_blk - 1) / cols_blk, a.heads, a.B);
-    if (r == 16) linear_recurrence_kernel<T, MODE, 16><<<grid, REC_THREADS, bytes(tc), stream>>>(a);
-    else linear_recurrence_kernel<T, MODE, 32><<<grid, REC_THREADS, bytes(tc), stream>>>(a);
+    auto kernel = r == 16 ? linear_recurrence_kernel<T, MODE, 16> : linear_recurrence_kernel<T, MODE, 32>;
+    static size_t allowed[2] = {48 * 1024, 48 * 1024};       // per instantiation (r == 16, r == 32): raised once, outside any capture
+    size_t& cur = allowed[r == 16 ? 0 : 1];
+    if (bytes > cur) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        cur = 200 * 1024;
+    }
+    kernel<<<grid, REC_THREADS, bytes, stream>>>(a);
     return mixers_status();
 }
 

@@ -418,8 +418,9 @@ class WindowKVLayer(NormalKVLayer):
 
 class RecurrentStateLayer:
     """What a linear recurrence carries from token to token: the matrix state [B, H, D, Dv] in 32-bit floats and, where a
-    short convolution precedes it, the last ``taps - 1`` inputs of every channel [B, taps - 1, C].  The convolution kernel reads
-    one tail buffer and writes the other (``flip_tail``), so that no thread reads what another has replaced."""
+    short convolution precedes it, the last ``taps - 1`` inputs of every channel [B, taps - 1, C].  Over several new tokens the
+    convolution kernel reads ``tail`` and writes ``tail_next`` (no thread reads what another has replaced) and the caller copies
+    it back; ``tail`` itself never moves."""
 
     def __init__(self):
         self.state = None
@@ -436,9 +437,6 @@ class RecurrentStateLayer:
             self.tail = torch.zeros(batch, max(taps - 1, 1), channels, dtype=dtype, device=device)
             self.tail_next = torch.empty_like(self.tail)
         return self.tail, self.tail_next
-
-    def flip_tail(self):
-        self.tail, self.tail_next = self.tail_next, self.tail
 
     def clear(self):
         for t in (self.state, self.tail, self.tail_next):

@@ -260,7 +260,7 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
             conv = ops.short_conv_silu(proj, off_r, C, r.conv_weight, tail, tail, cache.seen, pad)
         else:
             conv = ops.short_conv_silu(proj, off_r, C, r.conv_weight, tail, tail_next, cache.seen, pad)
-            st.rec.flip_tail()
+            tail.copy_(tail_next)                                            # the tail keeps its address (a recorded step holds it)
         state = st.rec.matrix(B, r.heads, r.dim, r.vdim, h.device)
         o = ops.gated_delta_rule(conv, r.kv_heads, r.heads, r.dim, r.vdim, proj, off_b, off_a, r.A_log, r.dt_bias, state,
                                  cache.seen, pad)
