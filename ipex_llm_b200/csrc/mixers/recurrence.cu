@@ -71,11 +71,12 @@ struct RecStage {
     static __host__ __device__ size_t floats(int tc, int dp, int cols_blk) { return (size_t)tc * ((MODE == 1 ? 3 : 2) * dp + cols_blk + 4); }
 };
 
-// producers: tokens t0 .. t0 + nt - 1 of the call into one stage.  A warp takes up to REC_TPW tokens at once so that their loads
-// are in flight together and their reductions overlap.
+// producers: tokens t0 .. t0 + nt - 1 of the call into one stage.  A warp takes up to REC_TPW tokens at once, and EVERY global
+// load of its share (q, k and decay rows 128 elements at a time, the tokens' scalars one lane each, the first values) is issued
+// before the first use of any: a warp issues in order, so each wait on memory would otherwise be paid in full, ~20 times a stage.
 template <typename T, int MODE>
 __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE> st, int b, int h, int qh, int t0, int nt, int dp, int cols_blk,
-                                                 int col0, int ptid) {
+                                                 int col0, int ptid, float neg_exp_a, float dt_bias) {
     const int lane = ptid & 31, pw = ptid >> 5;
     const int dim = a.dim, S = a.S;
     const T* src = (const T*)a.src;
@@ -83,33 +84,61 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
     const int tt0 = pw * REC_TPW;
     int cnt = nt - tt0;
     if (cnt > REC_TPW) cnt = REC_TPW;
+    // the block's value columns: the first (usually only) batch of loads goes out now and is stored at the end
+    constexpr int VB = 4;
+    const int nv = nt * cols_blk;
+    float vreg[VB];
+#pragma unroll
+    for (int e = 0; e < VB; ++e) {
+        int i = ptid + e * REC_PRODUCERS;
+        vreg[e] = 0.0f;
+        if (i < nv) {
+            int tt = i / cols_blk, cg = col0 + (i - tt * cols_blk);
+            if (cg < a.vdim) vreg[e] = to_f(src[((long)b * S + t0 + tt) * a.ld_src + a.off_v + h * a.vdim + cg]);
+        }
+    }
+    float lb = 0.0f, la = 0.0f;                              // lane j: the gate logits of the warp's token j
+    if (MODE == 0 && lane < cnt) {
+        const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt0 + lane) * a.ld_proj;
+        lb = to_f(pr[a.off_b + h]);
+        la = to_f(pr[a.off_a + h]);
+    }
     if (cnt > 0) {
         float sq[REC_TPW], sk[REC_TPW], skq[REC_TPW];
 #pragma unroll
         for (int j = 0; j < REC_TPW; ++j) sq[j] = sk[j] = skq[j] = 0.0f;
-        for (int i = lane; i < dp; i += 32) {
-            float qv[REC_TPW], kv[REC_TPW];
+        for (int blk = 0; blk < dp; blk += 128) {
+            float qv[REC_TPW][4], kv[REC_TPW][4], zv[REC_TPW][4];
 #pragma unroll
             for (int j = 0; j < REC_TPW; ++j) {
-                qv[j] = kv[j] = 0.0f;
-                if (j < cnt && i < dim) {
-                    const T* row = src + ((long)b * S + t0 + tt0 + j) * a.ld_src;
-                    qv[j] = to_f(row[a.off_q + qh * dim + i]);
-                    kv[j] = to_f(row[a.off_k + qh * dim + i]);
+                const T* row = src + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * a.ld_src;
+                const T* zr = MODE == 1 ? (const T*)a.z + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * ((long)a.heads * dim) + h * dim : nullptr;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = blk + lane + 32 * e;
+                    const bool ok = j < cnt && i < dim;
+                    qv[j][e] = ok ? to_f(row[a.off_q + qh * dim + i]) : 0.0f;
+                    kv[j][e] = ok ? to_f(row[a.off_k + qh * dim + i]) : 0.0f;
+                    if (MODE == 1) zv[j][e] = ok ? to_f(zr[i]) : 0.0f;
                 }
             }
 #pragma unroll
             for (int j = 0; j < REC_TPW; ++j) {
                 if (j < cnt) {
-                    if (MODE == 1) {
-                        const T* zr = (const T*)a.z + ((long)b * S + t0 + tt0 + j) * ((long)a.heads * dim) + h * dim;
-                        st.a[(tt0 + j) * dp + i] = i < dim ? expf(log_sigmoid_f(to_f(zr[i])) * a.inv_tau) : 1.0f;
-                        st.q[(tt0 + j) * dp + i] = qv[j] * q_scale;
-                    } else {
-                        st.q[(tt0 + j) * dp + i] = qv[j];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = blk + lane + 32 * e;
+                        if (i < dp) {
+                            if (MODE == 1) {
+                                st.a[(tt0 + j) * dp + i] = i < dim ? expf(log_sigmoid_f(zv[j][e]) * a.inv_tau) : 1.0f;
+                                st.q[(tt0 + j) * dp + i] = qv[j][e] * q_scale;
+                            } else {
+                                st.q[(tt0 + j) * dp + i] = qv[j][e];
+                            }
+                            st.k[(tt0 + j) * dp + i] = kv[j][e];
+                            sq[j] += qv[j][e] * qv[j][e]; sk[j] += kv[j][e] * kv[j][e]; skq[j] += qv[j][e] * kv[j][e];
+                        }
                     }
-                    st.k[(tt0 + j) * dp + i] = kv[j];
-                    sq[j] += qv[j] * qv[j]; sk[j] += kv[j] * kv[j]; skq[j] += qv[j] * kv[j];
                 }
             }
         }
@@ -117,26 +146,29 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
 #pragma unroll
             for (int j = 0; j < REC_TPW; ++j) { sq[j] = warp_sum(sq[j]); sk[j] = warp_sum(sk[j]); skq[j] = warp_sum(skq[j]); }
             __syncwarp();
+            float my_nq = 0.0f, my_nk = 0.0f, my_kq = 0.0f;
 #pragma unroll
             for (int j = 0; j < REC_TPW; ++j) {
                 if (j < cnt) {
                     const float nq = q_scale / sqrtf(sq[j] + 1e-6f), nk = 1.0f / sqrtf(sk[j] + 1e-6f);
                     for (int i = lane; i < dp; i += 32) { st.q[(tt0 + j) * dp + i] *= nq; st.k[(tt0 + j) * dp + i] *= nk; }
-                    if (lane == 0) {
-                        const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt0 + j) * a.ld_proj;
-                        float beta = sigmoid_f(to_f(pr[a.off_b + h]));
-                        float dt = softplus_f(to_f(pr[a.off_a + h]) + to_f(((const T*)a.dt_bias)[h]));
-                        st.sc[(tt0 + j) * 4 + 0] = expf(-expf(to_f(((const T*)a.A_log)[h])) * dt);
-                        st.sc[(tt0 + j) * 4 + 1] = beta;
-                        st.sc[(tt0 + j) * 4 + 2] = skq[j] * nq * nk;
-                    }
+                    if (lane == j) { my_nq = nq; my_nk = nk; my_kq = skq[j]; }
                 }
+            }
+            if (lane < cnt) {
+                st.sc[(tt0 + lane) * 4 + 0] = expf(neg_exp_a * softplus_f(la + dt_bias));
+                st.sc[(tt0 + lane) * 4 + 1] = sigmoid_f(lb);
+                st.sc[(tt0 + lane) * 4 + 2] = my_kq * my_nq * my_nk;
             }
         }
     }
-    for (int i = ptid; i < nt * cols_blk; i += REC_PRODUCERS) {
-        int tt = i / cols_blk, cl = i - tt * cols_blk;
-        int cg = col0 + cl;
+#pragma unroll
+    for (int e = 0; e < VB; ++e) {
+        int i = ptid + e * REC_PRODUCERS;
+        if (i < nv) st.v[i] = vreg[e];
+    }
+    for (int i = ptid + VB * REC_PRODUCERS; i < nv; i += REC_PRODUCERS) {          // narrow heads only: more columns than one batch
+        int tt = i / cols_blk, cg = col0 + (i - tt * cols_blk);
         st.v[i] = cg < a.vdim ? to_f(src[((long)b * S + t0 + tt) * a.ld_src + a.off_v + h * a.vdim + cg]) : 0.0f;
     }
 }
@@ -173,9 +205,14 @@ __global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs 
         for (int t = 0; t < first; ++t) obase[(long)t * a.heads * vdim + col] = 0.0f;
 
     const int nchunks = (S - first + tc - 1) / tc;
+    float neg_exp_a = 0.0f, dt_bias = 0.0f;
+    if (MODE == 0 && producer) {
+        neg_exp_a = -expf(to_f(((const T*)a.A_log)[h]));
+        dt_bias = to_f(((const T*)a.dt_bias)[h]);
+    }
     if (producer && nchunks > 0)
         rec_stage_tokens<T, MODE>(a, RecStage<MODE>(sh, tc, dp, cols_blk), b, h, qh, first, (S - first < tc ? S - first : tc), dp, cols_blk, col0,
-                                  tid - REC_CONSUMERS);
+                                  tid - REC_CONSUMERS, neg_exp_a, dt_bias);
     __syncthreads();
     for (int ci = 0; ci < nchunks; ++ci) {
         const int t0 = first + ci * tc;
@@ -183,7 +220,7 @@ __global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs 
             if (ci + 1 < nchunks) {
                 const int t1 = t0 + tc;
                 rec_stage_tokens<T, MODE>(a, RecStage<MODE>(sh + ((ci + 1) & 1) * stage_floats, tc, dp, cols_blk), b, h, qh, t1,
-                                          (S - t1 < tc ? S - t1 : tc), dp, cols_blk, col0, tid - REC_CONSUMERS);
+                                          (S - t1 < tc ? S - t1 : tc), dp, cols_blk, col0, tid - REC_CONSUMERS, neg_exp_a, dt_bias);
             }
         } else {
             // the tokens in order; a column's lanes only talk to each other.  Four partial sums per dot product keep the
@@ -233,8 +270,147 @@ __global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs 
     }
 }
 
+// ---- a few new tokens (decoding, short portions): no pipeline to fill.  The whole block stages up to tc tokens, then every
+// thread runs them on its rows of its column; 128 threads and half the registers of the pipelined kernel, so that the
+// many small blocks of a decode step (batch x heads x column blocks) are resident together.
+constexpr int REC_FEW_THREADS = 128;
+
+template <typename T, int MODE, int R>
+__global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(RecArgs a) {
+    extern __shared__ float sh[];
+    const int lpc = a.lpc, dp = R * lpc, tc = a.tc;
+    const int cols_blk = REC_FEW_THREADS / lpc;
+    float* kbuf = sh;                                        // [tc][dp]
+    float* qbuf = kbuf + tc * dp;                            // [tc][dp]
+    float* abuf = qbuf + tc * dp;                            // [tc][dp] (gla only)
+    float* vbuf = abuf + (MODE == 1 ? tc * dp : 0);          // [tc][cols_blk]
+    float* sc = vbuf + tc * cols_blk;                        // [tc][4]: g, beta, k.q
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int sub = tid % lpc;
+    const int col_l = tid / lpc;
+    const int col = blockIdx.x * cols_blk + col_l;
+    const bool col_ok = col < a.vdim;
+    const int dim = a.dim, vdim = a.vdim, S = a.S;
+    const int qh = h / (a.heads / a.q_heads);
+    const T* src = (const T*)a.src;
+
+    float M[R];
+    float* st = a.state + ((long)b * a.heads + h) * dim * vdim;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        int i = r * lpc + sub;
+        M[r] = (col_ok && i < dim) ? st[(long)i * vdim + col] : 0.0f;
+    }
+    int first = a.pad ? a.pad[b] - a.slot0 : 0;
+    if (first < 0) first = 0;
+    if (first > S) first = S;
+    float* obase = a.o + (((long)b * S) * a.heads + h) * vdim;
+    if (sub == 0 && col_ok)
+        for (int t = 0; t < first; ++t) obase[(long)t * a.heads * vdim + col] = 0.0f;
+    const float q_scale = rsqrtf((float)dim);
+
+    for (int t0 = first; t0 < S; t0 += tc) {
+        const int nt = S - t0 < tc ? S - t0 : tc;
+        __syncthreads();
+        // ---- stage nt tokens: a warp per token
+        for (int tt = wid; tt < nt; tt += REC_FEW_THREADS / 32) {
+            const T* row = src + ((long)b * S + t0 + tt) * a.ld_src;
+            const T* qr = row + a.off_q + qh * dim;
+            const T* kr = row + a.off_k + qh * dim;
+            float sq = 0.0f, sk = 0.0f, skq = 0.0f;
+            for (int i = lane; i < dp; i += 32) {
+                float qv = i < dim ? to_f(qr[i]) : 0.0f, kv = i < dim ? to_f(kr[i]) : 0.0f;
+                qbuf[tt * dp + i] = qv;
+                kbuf[tt * dp + i] = kv;
+                sq += qv * qv; sk += kv * kv; skq += qv * kv;
+            }
+            if (MODE == 0) {
+                sq = warp_sum(sq); sk = warp_sum(sk); skq = warp_sum(skq);
+                const float nq = q_scale / sqrtf(sq + 1e-6f), nk = 1.0f / sqrtf(sk + 1e-6f);
+                __syncwarp();
+                for (int i = lane; i < dp; i += 32) { qbuf[tt * dp + i] *= nq; kbuf[tt * dp + i] *= nk; }
+                if (lane == 0) {
+                    const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt) * a.ld_proj;
+                    float beta = sigmoid_f(to_f(pr[a.off_b + h]));
+                    float dt = softplus_f(to_f(pr[a.off_a + h]) + to_f(((const T*)a.dt_bias)[h]));
+                    sc[tt * 4 + 0] = expf(-expf(to_f(((const T*)a.A_log)[h])) * dt);
+                    sc[tt * 4 + 1] = beta;
+                    sc[tt * 4 + 2] = skq * nq * nk;
+                }
+            } else {
+                const T* zr = (const T*)a.z + ((long)b * S + t0 + tt) * ((long)a.heads * dim) + h * dim;
+                for (int i = lane; i < dp; i += 32) {
+                    qbuf[tt * dp + i] *= q_scale;
+                    abuf[tt * dp + i] = i < dim ? expf(log_sigmoid_f(to_f(zr[i])) * a.inv_tau) : 1.0f;
+                }
+            }
+        }
+        for (int i = tid; i < nt * cols_blk; i += REC_FEW_THREADS) {
+            int tt = i / cols_blk, cl = i - tt * cols_blk;
+            int cg = blockIdx.x * cols_blk + cl;
+            vbuf[i] = cg < vdim ? to_f(src[((long)b * S + t0 + tt) * a.ld_src + a.off_v + h * vdim + cg]) : 0.0f;
+        }
+        __syncthreads();
+        // ---- the tokens in order; a column's lanes only talk to each other
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* kk = kbuf + tt * dp + sub;
+            const float* qq = qbuf + tt * dp + sub;
+            const float v = vbuf[tt * cols_blk + col_l];
+            float o;
+            if (MODE == 0) {
+                float ak = 0.0f, cq = 0.0f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) { ak += M[r] * kk[r * lpc]; cq += M[r] * qq[r * lpc]; }
+                for (int m = lpc >> 1; m > 0; m >>= 1) { ak += __shfl_xor_sync(0xffffffffu, ak, m); cq += __shfl_xor_sync(0xffffffffu, cq, m); }
+                const float g = sc[tt * 4 + 0], beta = sc[tt * 4 + 1], kq = sc[tt * 4 + 2];
+                const float u = beta * (v - g * ak);
+                o = g * cq + kq * u;
+#pragma unroll
+                for (int r = 0; r < R; ++r) M[r] = g * M[r] + kk[r * lpc] * u;
+            } else {
+                const float* aa = abuf + tt * dp + sub;
+                o = 0.0f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) { M[r] = aa[r * lpc] * M[r] + kk[r * lpc] * v; o += M[r] * qq[r * lpc]; }
+                for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+            }
+            if (sub == 0 && col_ok) obase[(long)(t0 + tt) * a.heads * vdim + col] = o;
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            int i = r * lpc + sub;
+            if (i < dim) st[(long)i * vdim + col] = M[r];
+        }
+    }
+}
+
+
+template <typename T, int MODE>
+static int launch_recurrence_few(RecArgs a, cudaStream_t stream) {
+    int r = a.dim <= 512 ? 16 : 32;
+    int need = (a.dim + r - 1) / r;
+    int lpc = 1;
+    while (lpc < need) lpc <<= 1;
+    if (lpc > 32) return (int)cudaErrorInvalidValue;
+    int dp = r * lpc, cols_blk = REC_FEW_THREADS / lpc;
+    int arrays = MODE == 1 ? 3 : 2;
+    int tc = a.S < REC_TC ? a.S : REC_TC;
+    auto bytes = [&](int n) { return (size_t)n * (arrays * dp + cols_blk + 4) * sizeof(float); };
+    while (tc > 1 && bytes(tc) > 40 * 1024) tc >>= 1;
+    if (bytes(tc) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    a.lpc = lpc; a.tc = tc;
+    dim3 grid((a.vdim + cols_blk - 1) / cols_blk, a.heads, a.B);
+    if (r == 16) linear_recurrence_few_kernel<T, MODE, 16><<<grid, REC_FEW_THREADS, bytes(tc), stream>>>(a);
+    else linear_recurrence_few_kernel<T, MODE, 32><<<grid, REC_FEW_THREADS, bytes(tc), stream>>>(a);
+    return mixers_status();
+}
+
 template <typename T, int MODE>
 static int launch_recurrence(RecArgs a, cudaStream_t stream) {
+    if (a.S < REC_TC) return launch_recurrence_few<T, MODE>(a, stream);        // less than one stage of tokens
     int r = a.dim <= 512 ? 16 : 32;
     int need = (a.dim + r - 1) / r;
     int lpc = 1;

@@ -68,13 +68,16 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* 
     if constexpr (sizeof(T) == 2) {
         if ((dim & 7) == 0) {                                // rows start on 16-byte boundaries: eight elements a load
             const uint4* k4 = reinterpret_cast<const uint4*>(kr);
+            const float4* q4 = reinterpret_cast<const float4*>(qs);
+            float s0 = 0.0f, s1 = 0.0f;
             for (int d = 0; d < dim; d += 8) {
                 uint4 v = k4[d >> 3];
                 const T* e = reinterpret_cast<const T*>(&v);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s += qs[d + i] * to_f(e[i]);
+                float4 qa = q4[d >> 2], qb = q4[(d >> 2) + 1];
+                s0 += qa.x * to_f(e[0]) + qa.y * to_f(e[1]) + qa.z * to_f(e[2]) + qa.w * to_f(e[3]);
+                s1 += qb.x * to_f(e[4]) + qb.y * to_f(e[5]) + qb.z * to_f(e[6]) + qb.w * to_f(e[7]);
             }
-            return s;
+            return s0 + s1;
         }
     }
     for (int d = 0; d < dim; ++d) s += qs[d] * to_f(kr[d]);
@@ -112,7 +115,51 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sigmoid_window_attention_kerne
     const T* kbase = k_store + ((long)b * kv_heads + g) * cap * dim;
     const T* vbase = v_store + ((long)b * kv_heads + g) * cap * vdim;
     const float bias = to_f(head_bias[h]);
-    for (int col0 = 0; col0 < vdim; col0 += VCOLS * 32) {
+    // 16-bit values in rows that start on 16-byte boundaries: a lane owns 8 neighbouring columns (one 16-byte load a key), the
+    // two halves of the warp take the even and the odd keys of a turn and meet at the end; 128 columns a pass
+    const bool wide = sizeof(T) == 2 && (vdim & 7) == 0;
+    for (int col0 = 0; wide && col0 < vdim; col0 += 128) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        const int mycol = col0 + (lane & 15) * 8;
+        const int half = lane >> 4;
+        for (int j0 = lo + 32 * wid; j0 <= c; j0 += 32 * ATT_WARPS) {
+            const int j = j0 + lane;
+            float wgt = 0.0f;
+            if (j <= c) wgt = sigmoid_f(dot_row(qs, kbase + (long)j * dim, dim) * scale + bias);
+            const int nk = c - j0 + 1 < 32 ? c - j0 + 1 : 32;
+            for (int jj = 0; jj < nk; jj += 2) {             // keys past the end carry weight 0; their row index is clamped
+                const int mine = jj + half;
+                const float wj = __shfl_sync(0xffffffffu, wgt, mine & 31);
+                if (mycol < vdim) {
+                    const int row = j0 + mine <= c ? j0 + mine : c;
+                    uint4 v = *reinterpret_cast<const uint4*>(vbase + (long)row * vdim + mycol);
+                    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] += wj * to_f(e[i]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+        if (lane < 16) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) part[wid * 128 + lane * 8 + i] = acc[i];
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < 128; e += blockDim.x) {
+            const int col = col0 + e;
+            if (col < vdim) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < ATT_WARPS; ++w) sum += part[w * 128 + e];
+                dst[col] = from_f<T>(sum * out_scale);
+            }
+        }
+        __syncthreads();
+    }
+    for (int col0 = 0; !wide && col0 < vdim; col0 += VCOLS * 32) {
         float acc[VCOLS];
 #pragma unroll
         for (int i = 0; i < VCOLS; ++i) acc[i] = 0.0f;

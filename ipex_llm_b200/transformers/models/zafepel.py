@@ -330,7 +330,9 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
             idx = slice(-logits_to_keep, None) if isinstance(logits_to_keep, int) else logits_to_keep.to(dev)
             xk = x.view(B, S, -1)[:, idx, :].contiguous()
             h = ops.dyt_residual_norm(xk.view(-1, xk.shape[-1]), None, None, core.norm, dtype).view(B, xk.shape[1], -1)
-        logits = _lin(self.lm_head, h.reshape(-1, h.shape[-1]))
+        # every kept position as a row of its own ([rows, 1, W]): a converted lm_head keeps only the last position of a long
+        # sequence axis (the reference's prefill shortcut), and which positions to keep is decided here, by logits_to_keep
+        logits = _lin(self.lm_head, h.reshape(-1, 1, h.shape[-1]))
         logits = ops.soft_cap(logits, cfg.logit_softcap).view(B, h.shape[1], -1)          # fp32
         return CausalLMOutputWithPast(logits=logits, past_key_values=cache)
 

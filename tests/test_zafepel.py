@@ -267,10 +267,11 @@ def test_window_attention_alone(mixers, cuda_device, dtype, tol, S, held):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("D,Dv,H,G", [(48, 32, 4, 2), (128, 128, 2, 1), (32, 80, 3, 3), (160, 16, 2, 2)])
-@pytest.mark.parametrize("S,held,window", [(70, 50, 40), (130, 0, 300), (16, 3, 7)])
+@pytest.mark.parametrize("S,held,window", [(70, 50, 40), (130, 0, 300), (16, 3, 7), (1, 300, 290), (5, 40, 33), (1, 6, 9)])
 def test_window_attention_many_tokens_16bit(mixers, cuda_device, dtype, D, Dv, H, G, S, held, window):
-    """the tensor-core path: head sizes that tile into 16s, portions that end inside a 64-row block, windows shorter and longer
-    than a block, padding, a filled cache in front"""
+    """the tensor-core path (16 tokens or more): head sizes that tile into 16s, portions that end inside a 64-row block, windows
+    shorter and longer than a block, padding, a filled cache in front; and the general kernel's 16-byte loads on the same head
+    sizes when a few tokens are decoded"""
     got, want = _attention_case(mixers, cuda_device, dtype, B=2, S=S, held=held, pad=[0, 5], H=H, G=G, D=D, Dv=Dv, rot_dims=16,
                                 window=window, seed=D + S)
     # keys and queries are rounded to 16 bits on the way (2^-9 relative each); the weights keep 16 bits
