@@ -127,6 +127,10 @@ class _BaseAutoModelClass:
         """MD:532-788: build the architecture on meta, size the packed buffers
         (``convert_shape_only``), then install the saved canonical bytes."""
         from ipex_llm_b200.transformers.convert import ggml_convert_low_bit
+        native = native_architecture(pretrained_model_name_or_path)
+        if native is not None:                           # importing the defining module registers it with the Auto classes
+            import importlib
+            importlib.import_module(native)
         config = transformers.AutoConfig.from_pretrained(pretrained_model_name_or_path)
         low_bit = config.to_dict().get("bigdl_transformers_low_bit", False)
         invalidInputError(low_bit, "Detect this model is not a low-bit model, Please use from_pretrained "

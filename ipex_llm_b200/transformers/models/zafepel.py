@@ -33,8 +33,12 @@ class ZafepelConfig(PreTrainedConfig):
     ``loop`` (``start``, ``stop``, ``times``; optional), ``norm.eps``, ``logit_softcap`` (optional)."""
     model_type = "zafepel"
 
-    def __init__(self, vocab=256, width=64, layers=None, loop=None, norm=None, logit_softcap=None, architecture="Zafepel", **kwargs):
+    def __init__(self, vocab=256, width=64, layers=None, loop=None, norm=None, logit_softcap=None, architecture="Zafepel",
+                 gla_ranks=None, **kwargs):
         self.vocab, self.width = int(vocab), int(width)
+        # the rank of each gla layer's decay projection: not a key of the design's config.json (the loader reads it off the
+        # checkpoint's shapes); kept here so that a saved model can be rebuilt from its configuration alone
+        self.gla_ranks = {str(k): int(v) for k, v in (gla_ranks or {}).items()}
         self.layers = layers or []
         self.loop = loop
         self.norm = norm or {"eps": 1e-6}
@@ -210,7 +214,10 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
 
     def __init__(self, config: ZafepelConfig, ranks=None):
         super().__init__(config)
-        self.model = ZafepelModel(config, ranks or {})
+        if ranks is None:
+            ranks = {int(k): v for k, v in config.gla_ranks.items()}
+        config.gla_ranks = {str(k): int(v) for k, v in ranks.items()}
+        self.model = ZafepelModel(config, ranks)
         self.lm_head = nn.Linear(config.width, config.vocab, bias=False)
         self.collect_residual = None          # a list: gets the residual stream after every layer run (debugging aid)
 
@@ -432,6 +439,20 @@ def load_pretrained(model_dir, torch_dtype=None, device=None):
     model.load_state_dict(state, strict=True, assign=True)
     model.eval()
     model.requires_grad_(False)
+    model.config.dtype = torch_dtype
     if device is not None:
         model = model.to(device)
     return model
+
+
+# the loaders that go through transformers' Auto classes (load_low_bit builds the architecture from a saved configuration)
+def _register():
+    from transformers import AutoConfig, AutoModelForCausalLM
+    try:
+        AutoConfig.register("zafepel", ZafepelConfig)
+        AutoModelForCausalLM.register(ZafepelConfig, ZafepelForCausalLM)
+    except ValueError:                                                       # registered already
+        pass
+
+
+_register()

@@ -581,3 +581,27 @@ def test_greedy_generate_matches_the_oracle(models, cuda_device):
             lg = om.forward(torch.tensor([[picked[-1]]]), st)
         n_sure = next((j for j, m in enumerate(margins) if m < 1e-3), new)      # a tie in the oracle decides nothing
         assert out[i, width:width + n_sure].tolist() == picked[:n_sure]
+
+
+@pytest.mark.gpu
+def test_low_bit_conversion_save_and_load(tmp_path, cuda_device, native_lib):
+    """the projections are ordinary linears to the converter: sym_int4 through from_pretrained, then save_low_bit / load_low_bit"""
+    from ipex_llm_b200.transformers import AutoModelForCausalLM
+    from ipex_llm_b200.transformers.low_bit_linear import LowBitLinear
+    cfg = O.random_config(0, width=128, ff=192, heads=4, kv_heads=2, dim=16, vdim=16, rot_dims=8, r_heads=4, r_kv_heads=2, r_dim=16,
+                          r_vdim=16, g_heads=2, g_dim=16, g_vdim=32, rank=4)
+    w = O.random_weights(cfg, 5)
+    save_checkpoint(cfg, w, tmp_path / "m")
+    toks = torch.tensor([_tokens(cfg, 19, 7)], device=cuda_device)
+    dense = load_framework(tmp_path / "m", torch.bfloat16, cuda_device)
+    low = AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), load_in_low_bit="sym_int4", torch_dtype=torch.bfloat16).to(cuda_device)
+    converted = [n for n, m in low.named_modules() if isinstance(m, LowBitLinear)]
+    assert any(n.endswith("in_proj") for n in converted) and any(n.endswith("down_proj") for n in converted) and "lm_head" in converted
+    with torch.no_grad():
+        a, b = dense(input_ids=toks).logits[0].cpu(), low(input_ids=toks).logits[0].cpu()
+    assert torch.isfinite(b).all() and logits_error(b, a) < 0.5           # 4-bit weights: close, not equal
+    low.save_low_bit(str(tmp_path / "lb"))
+    back = AutoModelForCausalLM.load_low_bit(str(tmp_path / "lb")).to(cuda_device)
+    with torch.no_grad():
+        c = back(input_ids=toks).logits[0].cpu()
+    assert logits_error(c, b) < 1e-3
