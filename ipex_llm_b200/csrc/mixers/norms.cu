@@ -13,22 +13,20 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int64_t* __
     }
 }
 
+// one block row per token (blockIdx.x), columns across the block and blockIdx.y
 template <typename T>
 __global__ void dyt_residual_norm_kernel(float* __restrict__ x, long n_rows, int width, const T* __restrict__ y, const T* __restrict__ post_w,
                                          const T* __restrict__ post_b, const T* __restrict__ post_alpha, const T* __restrict__ add,
                                          const T* __restrict__ pre_w, const T* __restrict__ pre_b, const T* __restrict__ pre_alpha,
                                          T* __restrict__ out) {
-    const float pa = y ? to_f(post_alpha[0]) : 0.0f;
-    const float a = out ? to_f(pre_alpha[0]) : 0.0f;
-    long total = n_rows * (long)width;
-    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-        int c = (int)(i % width);
-        float v = x[i];
-        if (y) v += tanhf(pa * to_f(y[i])) * to_f(post_w[c]) + to_f(post_b[c]);
-        if (add) v += to_f(add[c]);
-        if (y || add) x[i] = v;
-        if (out) out[i] = from_f<T>(tanhf(a * v) * to_f(pre_w[c]) + to_f(pre_b[c]));
-    }
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const long i = (long)blockIdx.x * width + c;
+    float v = x[i];
+    if (y) v += tanhf(to_f(post_alpha[0]) * to_f(y[i])) * to_f(post_w[c]) + to_f(post_b[c]);
+    if (add) v += to_f(add[c]);
+    if (y || add) x[i] = v;
+    if (out) out[i] = from_f<T>(tanhf(to_f(pre_alpha[0]) * v) * to_f(pre_w[c]) + to_f(pre_b[c]));
 }
 
 // one warp per (row, head)
@@ -101,7 +99,9 @@ extern "C" int mixers_dyt_residual_norm(int dtype, float* x, long n_rows, int wi
                                         const void* post_alpha, const void* add, const void* pre_w, const void* pre_b, const void* pre_alpha,
                                         void* out, mixers_stream_t stream) {
     if (n_rows <= 0 || (!y && !add && !out)) return 0;
-    MIXERS_DISPATCH(dtype, dyt_residual_norm_kernel<T><<<grid_for(n_rows * width, 256), 256, 0, (cudaStream_t)stream>>>(
+    const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+    dim3 blocks((unsigned)n_rows, (unsigned)((width + threads - 1) / threads));
+    MIXERS_DISPATCH(dtype, dyt_residual_norm_kernel<T><<<blocks, threads, 0, (cudaStream_t)stream>>>(
         x, n_rows, width, (const T*)y, (const T*)post_w, (const T*)post_b, (const T*)post_alpha, (const T*)add, (const T*)pre_w,
         (const T*)pre_b, (const T*)pre_alpha, (T*)out));
     return mixers_status();

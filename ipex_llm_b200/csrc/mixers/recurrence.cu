@@ -12,29 +12,30 @@
 // which is the same arithmetic reordered so that one round of shuffles serves both.
 #include "mixers_common.cuh"
 
+// one block row per token (blockIdx.x), channels across the block and blockIdx.y: no index division in the loop
 template <typename T>
 __global__ void short_conv_silu_kernel(const T* __restrict__ proj, int B, int S, int ld, int off, int C, int taps, const T* __restrict__ w,
                                        const T* __restrict__ tail, T* __restrict__ tail_next, int slot0, const int32_t* __restrict__ pad,
                                        T* __restrict__ y) {
-    long total = (long)B * S * C;
     const int tl = taps - 1 > 0 ? taps - 1 : 1;             // rows of a tail buffer
-    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-        int c = (int)(i % C);
-        long n = i / C;
-        int b = (int)(n / S), t = (int)(n - (long)b * S);
-        int first = pad ? pad[b] - slot0 : 0;                // new tokens before this index are padding
-        if (first < 0) first = 0;
-        auto input = [&](int tt) -> float {
-            if (tt < 0) return to_f(tail[((long)b * tl + (taps - 1 + tt)) * C + c]);
-            if (tt < first) return 0.0f;
-            return to_f(proj[((long)b * S + tt) * ld + off + c]);
-        };
-        float acc = 0.0f;
-        for (int j = 0; j < taps; ++j) acc += to_f(w[(long)c * taps + j]) * input(t - (taps - 1) + j);
-        y[i] = from_f<T>(t < first ? 0.0f : silu_f(acc));
-        if (t == S - 1)
-            for (int r = 0; r < taps - 1; ++r) tail_next[((long)b * tl + r) * C + c] = from_f<T>(input(S - (taps - 1) + r));
-    }
+    const int n = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int b = n / S, t = n - b * S;
+    int first = pad ? pad[b] - slot0 : 0;                    // new tokens before this index are padding
+    if (first < 0) first = 0;
+    const T* in = proj + (long)b * S * ld + off + c;
+    const T* tb = tail + (long)b * tl * C + c;
+    auto input = [&](int tt) -> float {
+        if (tt < 0) return to_f(tb[(long)(taps - 1 + tt) * C]);
+        if (tt < first) return 0.0f;
+        return to_f(in[(long)tt * ld]);
+    };
+    float acc = 0.0f;
+    for (int j = 0; j < taps; ++j) acc += to_f(w[(long)c * taps + j]) * input(t - (taps - 1) + j);
+    y[(long)n * C + c] = from_f<T>(t < first ? 0.0f : silu_f(acc));
+    if (t == S - 1)
+        for (int r = 0; r < taps - 1; ++r) tail_next[((long)b * tl + r) * C + c] = from_f<T>(input(S - (taps - 1) + r));
 }
 
 constexpr int REC_CONSUMERS = 128;                          // threads that own state columns (4 warps)
@@ -437,10 +438,9 @@ extern "C" int mixers_short_conv_silu(int dtype, const void* proj, int B, int S,
                                       const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream) {
     if (B <= 0 || S <= 0) return 0;
     if (taps < 1) return (int)cudaErrorInvalidValue;
-    long total = (long)B * S * C;
-    long g = (total + 255) / 256;
-    int blocks = (int)(g > 148L * 32 ? 148L * 32 : g);
-    MIXERS_DISPATCH(dtype, short_conv_silu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)proj, B, S, ld, off, C, taps, (const T*)w,
+    const int threads = C >= 256 ? 256 : ((C + 31) / 32) * 32;
+    dim3 blocks((unsigned)((long)B * S), (unsigned)((C + threads - 1) / threads));
+    MIXERS_DISPATCH(dtype, short_conv_silu_kernel<T><<<blocks, threads, 0, (cudaStream_t)stream>>>((const T*)proj, B, S, ld, off, C, taps, (const T*)w,
                                                                                                  (const T*)tail, (T*)tail_next, slot0, pad, (T*)y));
     return mixers_status();
 }
