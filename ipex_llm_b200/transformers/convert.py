@@ -162,8 +162,9 @@ def _optimize_pre(model, qtype=None):
         model.apply(merge_qkv)
     elif model_type == "zafepel":
         # every projection that reads a mixer's input -> one in_proj; a parallel mixer's two output projections -> one out_proj
+        import functools
         from ipex_llm_b200.transformers.models.zafepel import merge_projections
-        model.apply(merge_projections)
+        model.apply(functools.partial(merge_projections, row_multiple=128 if qtype is not None else 0))
     return model
 
 

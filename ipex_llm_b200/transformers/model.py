@@ -59,8 +59,9 @@ class _BaseAutoModelClass:
     HF_MODEL = None
 
     @classmethod
-    def _load_base(cls, *args, **kwargs):
-        """the unconverted model: one of this package's own designs by config.json, else Hugging Face's class"""
+    def _load_base(cls, *args, low_bit_qtype=None, **kwargs):
+        """the unconverted model: one of this package's own designs by config.json, else Hugging Face's class.
+        ``low_bit_qtype``: the format the linears will be converted to afterwards (the merge of projections prepares for it)"""
         path = args[0] if args else kwargs.get("pretrained_model_name_or_path")
         native = native_architecture(path) if path is not None else None
         if native is None:
@@ -70,7 +71,7 @@ class _BaseAutoModelClass:
         dtype = kwargs.get("torch_dtype", kwargs.get("dtype"))
         model = importlib.import_module(native).load_pretrained(path, torch_dtype=dtype)
         # such a model's forward runs on its merged projections only; the recorded decode step goes behind generate()
-        return _optimize_post(_optimize_pre(model))
+        return _optimize_post(_optimize_pre(model, low_bit_qtype))
 
     @classmethod
     def from_pretrained(cls, *args, **kwargs):
@@ -93,7 +94,7 @@ class _BaseAutoModelClass:
         """MD:436-530"""
         from ipex_llm_b200.transformers.convert import ggml_convert_low_bit
         invalidInputError(q_k in ggml_tensor_qtype, f"Unknown load_in_low_bit value: {q_k}")
-        model = cls._load_base(*args, **kwargs)
+        model = cls._load_base(*args, low_bit_qtype=ggml_tensor_qtype[q_k], **kwargs)
         model = model.to("cpu")
         model = ggml_convert_low_bit(model, ggml_tensor_qtype[q_k], optimize_model,
                                      modules_to_not_convert=modules_to_not_convert,

@@ -175,16 +175,31 @@ class ZafepelLayer(nn.Module):
             self.mlp = PolyNormMLP(width, lc["mlp"])
 
 
-def merge_projections(module: nn.Module):
+def _zero_rows(like: nn.Linear, rows_so_far: int, multiple: int):
+    """a bias-free projection of zeros that brings a merged row count up to a multiple (none when it is one already)"""
+    extra = -rows_so_far % multiple if multiple else 0
+    if not extra:
+        return []
+    with torch.device("meta"):
+        pad = nn.Linear(1, 1, bias=False)
+    pad.weight = nn.Parameter(torch.zeros(extra, like.weight.shape[1], dtype=like.weight.dtype, device=like.weight.device), requires_grad=False)
+    return [pad]
+
+
+def merge_projections(module: nn.Module, row_multiple: int = 0):
     """every projection that reads the mixer's input becomes one ``in_proj``; the two output projections of a parallel mixer
-    become one ``out_proj`` over the concatenated branch outputs"""
+    become one ``out_proj`` over the concatenated branch outputs.  ``row_multiple``: rows of zeros are appended to ``in_proj`` up
+    to a multiple of it (the low-bit prefill GEMM wants whole 128-row tiles; the few gate / rank rows would otherwise push the
+    whole projection onto the general path); the kernels address columns by offset, the extra ones are never read."""
     if isinstance(module, ParallelMixer) and not hasattr(module, "in_proj"):
         l, r = module.left, module.right
-        module.in_proj = merge_linear([l.q_proj, l.k_proj, l.v_proj, r.q_proj, r.k_proj, r.v_proj, r.b_proj, r.a_proj, r.g_proj])
+        parts = [l.q_proj, l.k_proj, l.v_proj, r.q_proj, r.k_proj, r.v_proj, r.b_proj, r.a_proj, r.g_proj]
+        module.in_proj = merge_linear(parts + _zero_rows(l.q_proj, sum(p.weight.shape[0] for p in parts), row_multiple))
         module.out_proj = merge_linear_inputs([l.o_proj, r.o_proj])
         del l.q_proj, l.k_proj, l.v_proj, l.o_proj, r.q_proj, r.k_proj, r.v_proj, r.b_proj, r.a_proj, r.g_proj, r.o_proj
     elif isinstance(module, GatedLinearAttention) and not hasattr(module, "in_proj"):
-        module.in_proj = merge_linear([module.q_proj, module.k_proj, module.v_proj, module.g_proj, module.a1_proj])
+        parts = [module.q_proj, module.k_proj, module.v_proj, module.g_proj, module.a1_proj]
+        module.in_proj = merge_linear(parts + _zero_rows(module.q_proj, sum(p.weight.shape[0] for p in parts), row_multiple))
         del module.q_proj, module.k_proj, module.v_proj, module.g_proj, module.a1_proj
 
 
@@ -281,7 +296,7 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
         qk, v = mx.heads * mx.dim, mx.heads * mx.vdim
         off_g = 2 * qk + v
         off_a1 = off_g + v
-        z = _lin(mx.a2_proj, proj[:, off_a1:])                               # [N, H * D] decay logits
+        z = _lin(mx.a2_proj, proj[:, off_a1:off_a1 + mx.a2_proj.in_features])  # [N, H * D] decay logits
         state = st.rec.matrix(B, mx.heads, mx.dim, mx.vdim, h.device)
         o = ops.gated_linear_attention(proj.view(B, S, P), mx.heads, mx.dim, mx.vdim, z.view(B, S, qk), mx.tau, state,
                                        cache.seen, cache.pad if cache.seen == 0 else None)
