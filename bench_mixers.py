@@ -162,7 +162,7 @@ def kernel_table(dev, dtype, peaks, timer):
         proj = rnd(B, S, P)
         cap = held + S
         ks, vs = rnd(B, KV_HEADS, cap, DIM), rnd(B, KV_HEADS, cap, DIM)
-        inv = torch.tensor([10000.0 ** (-2.0 * i / ROT_DIMS) for i in range(ROT_DIMS // 2)], device=dev)
+        inv = torch.tensor([10000.0 ** (-2.0 * i / ROT_DIMS) for i in range(ROT_DIMS // 2)], dtype=torch.float64, device=dev)
         qw, kw, hb = vec(DIM), vec(DIM), rnd(HEADS)
         prep = lambda: ops.window_qk_prepare(proj, 0, HEADS * DIM, (HEADS + KV_HEADS) * DIM, HEADS, KV_HEADS, DIM, DIM, qw, kw, 1e-5, inv,  # noqa: E731
                                              ROT_DIMS, ks, vs, cap, held, 0, pad)

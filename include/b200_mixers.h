@@ -28,12 +28,12 @@ int mixers_dyt_residual_norm(int dtype, float* x, long n_rows, int width, const 
                              void* out, mixers_stream_t stream);
 
 /* Queries, keys and values of new tokens taken from the columns of one projection output `proj` [B, S, ld]: per-head RMS norm
- * (weights q_w / k_w [dim]), rotation of the pairs (2i, 2i+1), i < rot_dims / 2, by position * inv_freq[i]; queries go to
+ * (weights q_w / k_w [dim]), rotation of the pairs (2i, 2i+1), i < rot_dims / 2, by position * inv_freq[i] (doubles: the angle is formed and its sine / cosine taken in double precision); queries go to
  * q_out float [B, S, heads, dim], keys and values into the caches k_store [B, kv_heads, cap, dim] / v_store [.., vdim] at
  * storage index held + t.  The token at storage index j sits in slot j + shift.  dyn (may be null): a device word that holds
  * `held` instead of the argument, for a step that is replayed from a CUDA graph while the cache grows. */
 int mixers_window_qk_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads,
-                             int kv_heads, int dim, int vdim, const void* q_w, const void* k_w, float eps, const float* inv_freq,
+                             int kv_heads, int dim, int vdim, const void* q_w, const void* k_w, float eps, const double* inv_freq,
                              int rot_dims, float* q_out, void* k_store, void* v_store, int cap, int held, int shift,
                              const int32_t* pad, const int32_t* dyn, mixers_stream_t stream);
 

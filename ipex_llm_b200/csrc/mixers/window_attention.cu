@@ -8,7 +8,7 @@
 template <typename T>
 __global__ void window_qk_prepare_kernel(const T* __restrict__ proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads, int kv_heads,
                                          int dim, int vdim, const T* __restrict__ q_w, const T* __restrict__ k_w, float eps,
-                                         const float* __restrict__ inv_freq, int rot_dims, float* __restrict__ q_out, T* __restrict__ k_store,
+                                         const double* __restrict__ inv_freq, int rot_dims, float* __restrict__ q_out, T* __restrict__ k_store,
                                          T* __restrict__ v_store, int cap, int held, int shift, const int32_t* __restrict__ pad,
                                          const int32_t* __restrict__ dyn) {
     if (dyn) held = dyn[0];                                 // the length lives on the device when the step is replayed from a graph
@@ -38,14 +38,17 @@ __global__ void window_qk_prepare_kernel(const T* __restrict__ proj, int B, int 
     const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
     float* qdst = is_q ? q_out + (n * heads + g) * (long)dim : nullptr;
     T* kdst = is_q ? nullptr : k_store + (((long)b * kv_heads + g) * cap + held + t) * dim;
-    const float fpos = (float)pos;
+    const double dpos = (double)pos;
     for (int p = lane; 2 * p < dim; p += 32) {
         int e0 = 2 * p, e1 = e0 + 1;
         float u = to_f(src[e0]) * inv * to_f(w[e0]);
         float v = e1 < dim ? to_f(src[e1]) * inv * to_f(w[e1]) : 0.0f;
         if (e0 < rot_dims) {                                // rot_dims is even: e1 is inside too
-            float sn, cs;
-            sincosf(fpos * inv_freq[p], &sn, &cs);
+            // the angle and its sine / cosine in double precision (a handful per head and token): at position 10^3 a 32-bit
+            // product position x frequency is already 6e-5 rad off
+            double dsn, dcs;
+            sincos(dpos * inv_freq[p], &dsn, &dcs);
+            const float sn = (float)dsn, cs = (float)dcs;
             float ru = u * cs - v * sn, rv = v * cs + u * sn;
             u = ru; v = rv;
         }
@@ -328,7 +331,9 @@ __global__ void __launch_bounds__(128) sigmoid_window_attention_tc_kernel(
             for (int i = 0; i < 4; ++i) {
                 const int j = jt + nt * 8 + 2 * tq + (i & 1);
                 const int r = i >> 1;
-                p[i] = (j >= row_lo[r] && j <= row_c[r]) ? sigmoid_f(sc[nt][i] * scale + bias) : 0.0f;
+                // hardware exponential and reciprocal (~2 ulp): these weights are split into two 16-bit parts right below,
+                // the exact division of sigmoid_f would cost more than the tile's MMAs
+                p[i] = (j >= row_lo[r] && j <= row_c[r]) ? __fdividef(1.0f, 1.0f + __expf(-(sc[nt][i] * scale + bias))) : 0.0f;
             }
             const int ks = nt >> 1, half = nt & 1;
 #pragma unroll
@@ -397,7 +402,7 @@ static int attention_tc(const float* q, const void* k_store, const void* v_store
 }
 
 extern "C" int mixers_window_qk_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads,
-                                        int kv_heads, int dim, int vdim, const void* q_w, const void* k_w, float eps, const float* inv_freq,
+                                        int kv_heads, int dim, int vdim, const void* q_w, const void* k_w, float eps, const double* inv_freq,
                                         int rot_dims, float* q_out, void* k_store, void* v_store, int cap, int held, int shift,
                                         const int32_t* pad, const int32_t* dyn, mixers_stream_t stream) {
     if (B <= 0 || S <= 0) return 0;

@@ -50,7 +50,7 @@ def window_qk_prepare(proj, off_q, off_k, off_v, heads, kv_heads, dim, vdim, q_w
     B, S, P = proj.shape
     invalidInputError(proj.is_contiguous() and k_store.is_contiguous() and v_store.is_contiguous() and k_store.shape[2] == cap
                       and v_store.shape[2] == cap
-                      and k_store.dtype == proj.dtype and v_store.dtype == proj.dtype and inv_freq.dtype == torch.float32,
+                      and k_store.dtype == proj.dtype and v_store.dtype == proj.dtype and inv_freq.dtype == torch.float64,
                       "window_qk_prepare: unexpected layout")
     if q is None:
         q = torch.empty(B, S, heads, dim, dtype=torch.float32, device=proj.device)

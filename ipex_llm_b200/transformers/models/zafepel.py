@@ -102,12 +102,12 @@ class SigmoidWindowAttention(nn.Module):
         self._inv_freq = {}
 
     def inv_freq(self, device):
-        """base^(-2i/rot_dims), i < rot_dims / 2: evaluated in double precision and rounded once to 32 bits.  Not a buffer:
-        ``model.to(dtype)`` must not round it again."""
+        """base^(-2i/rot_dims), i < rot_dims / 2, in double precision (the kernel forms the angles in double precision too).
+        Not a buffer: ``model.to(dtype)`` must not round it."""
         t = self._inv_freq.get(device)
         if t is None:
             freq = [self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)] or [0.0]    # never empty
-            t = self._inv_freq[device] = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
+            t = self._inv_freq[device] = torch.tensor(freq, dtype=torch.float64).to(device)
         return t
 
     def out_width(self):

@@ -228,7 +228,7 @@ def _attention_case(mixers, device, dtype, B, S, held, pad, H, G, D, Dv, rot_dim
         q_gain(proj_all)
     qw, kw = (torch.rand(D, generator=g) + 0.5).to(dtype), (torch.rand(D, generator=g) + 0.5).to(dtype)
     hb = (torch.randn(H, generator=g) - 0.5).to(dtype)
-    inv_freq = torch.tensor([50.0 ** (-2.0 * i / rot_dims) for i in range(rot_dims // 2)] or [0.0], dtype=F64).float()
+    inv_freq = torch.tensor([50.0 ** (-2.0 * i / rot_dims) for i in range(rot_dims // 2)] or [0.0], dtype=F64)
     pad_t = torch.tensor(pad, dtype=torch.int32)
     oq, ok, ov = 5, 5 + H * D, 5 + H * D + G * D
     scale = 1.3 / math.sqrt(D)
