@@ -419,7 +419,7 @@ static int launch_recurrence(RecArgs a, cudaStream_t stream) {
     if (lpc > 32) return (int)cudaErrorInvalidValue;         // heads wider than 1024 rows are not served
     int dp = r * lpc, cols_blk = REC_CONSUMERS / lpc;
     size_t bytes = 2 * RecStage<MODE>::floats(REC_TC, dp, cols_blk) * sizeof(float);      // two stages
-    if (bytes > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (bytes > 160 * 1024) return launch_recurrence_few<T, MODE>(a, stream);  // very wide heads: stages of fewer tokens, unpipelined
     a.lpc = lpc; a.tc = REC_TC;
     dim3 grid((a.vdim + cols_blk - 1) / cols_blk, a.heads, a.B);
     auto kernel = r == 16 ? linear_recurrence_kernel<T, MODE, 16> : linear_recurrence_kernel<T, MODE, 32>;

@@ -75,6 +75,11 @@ CONFIGS = {
     "flat": dict(width=64, vocab=50, order=("parallel", "parallel", "gla"), loop=None, window=64, heads=6, kv_heads=1, dim=20,
                  vdim=36, rot_dims=6, r_heads=6, r_kv_heads=3, r_dim=40, r_vdim=12, taps=1, g_heads=2, g_dim=33, g_vdim=70, rank=9,
                  ff=72, mlp_on=(True, True, False)),
+    # head sizes that tile into 16s (the tensor-core attention of a 16-bit model), a window shorter than a 64-row block,
+    # two passes of a three-layer block that ends at the last layer
+    "tile": dict(width=96, vocab=83, order=("gla", "parallel", "parallel"), loop=(0, 3, 2), window=21, heads=4, kv_heads=1, dim=32,
+                 vdim=48, rot_dims=32, r_heads=2, r_kv_heads=1, r_dim=32, r_vdim=16, taps=3, g_heads=2, g_dim=16, g_vdim=32, rank=6,
+                 ff=64, mlp_on=(True, False, False)),
 }
 
 
@@ -265,8 +270,17 @@ def test_window_attention_alone(mixers, cuda_device, dtype, tol, S, held):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("D,Dv,window,S,held", [(7, 300, 1, 20, 0), (300, 5, 2, 3, 40), (36, 520, 50, 33, 10), (2, 1, 3, 9, 0)])
+def test_window_attention_extreme_sizes_fp32(mixers, cuda_device, D, Dv, window, S, held):
+    """a window of one token (only itself), more value columns than one pass holds, heads wider than a warp's turn"""
+    got, want = _attention_case(mixers, cuda_device, torch.float32, B=2, S=S, held=held, pad=[1, 0], H=2, G=1, D=D, Dv=Dv,
+                                rot_dims=2 if D >= 2 else 0, window=window, seed=D)
+    assert (got - want).abs().max() < 3e-5 * max(1.0, want.abs().max())
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("D,Dv,H,G", [(48, 32, 4, 2), (128, 128, 2, 1), (32, 80, 3, 3), (160, 16, 2, 2)])
+@pytest.mark.parametrize("D,Dv,H,G", [(48, 32, 4, 2), (128, 128, 2, 1), (32, 80, 3, 3), (160, 16, 2, 2), (256, 256, 1, 1), (24, 264, 2, 1)])
 @pytest.mark.parametrize("S,held,window", [(70, 50, 40), (130, 0, 300), (16, 3, 7), (1, 300, 290), (5, 40, 33), (1, 6, 9)])
 def test_window_attention_many_tokens_16bit(mixers, cuda_device, dtype, D, Dv, H, G, S, held, window):
     """the tensor-core path (16 tokens or more): head sizes that tile into 16s, portions that end inside a 64-row block, windows
@@ -313,7 +327,7 @@ def test_window_attention_after_trim(mixers, cuda_device):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("taps", [1, 2, 4])
+@pytest.mark.parametrize("taps", [1, 2, 4, 9])
 def test_short_conv_in_portions(mixers, cuda_device, dtype, tol, taps):
     g = torch.Generator().manual_seed(taps)
     B, total, C, off, P = 2, 13, 11, 3, 20
@@ -356,7 +370,8 @@ def _delta_oracle(conv, proj, A_log, dtb, G, H, D, Dv, pad):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-5)])     # inputs are rounded, the recurrence is 32-bit
-@pytest.mark.parametrize("G,H,D,Dv", [(1, 3, 5, 9), (2, 2, 40, 33), (2, 4, 16, 130), (1, 1, 70, 3)])
+@pytest.mark.parametrize("G,H,D,Dv", [(1, 3, 5, 9), (2, 2, 40, 33), (2, 4, 16, 130), (1, 1, 70, 3), (1, 2, 200, 20), (1, 1, 600, 40),
+                                       (1, 1, 1024, 8)])
 def test_delta_rule_alone_and_in_portions(mixers, cuda_device, dtype, tol, G, H, D, Dv):
     B, total = 2, 37
     conv, proj, A_log, dtb = _delta_inputs(B, total, G, H, D, Dv, 17, dtype)
@@ -405,7 +420,7 @@ def test_delta_rule_remembers_a_far_token(mixers, cuda_device):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,D,Dv", [(3, 7, 5), (1, 33, 70), (2, 64, 16)])
+@pytest.mark.parametrize("H,D,Dv", [(3, 7, 5), (1, 33, 70), (2, 64, 16), (1, 300, 24), (1, 520, 136)])
 def test_gated_linear_attention_alone_and_in_portions(mixers, cuda_device, dtype, H, D, Dv):
     g = torch.Generator().manual_seed(23)
     B, total, tau = 2, 29, 6.0
@@ -454,7 +469,7 @@ def _tokens(cfg, n, seed):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["odd", "plain", "flat"])
+@pytest.mark.parametrize("name", ["odd", "plain", "flat", "tile"])
 def test_whole_prompt_matches_the_oracle_fp32(models, cuda_device, name):
     cfg, w, model = models(name, torch.float32)
     toks = _tokens(cfg, 23, 1)
@@ -474,14 +489,18 @@ def test_whole_prompt_matches_the_oracle_fp32(models, cuda_device, name):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["odd", "plain"])
+@pytest.mark.parametrize("name", ["odd", "plain", "tile"])
 def test_whole_prompt_matches_the_oracle_bf16(models, cuda_device, name):
     cfg, w, model = models(name, torch.bfloat16)
-    toks = _tokens(cfg, 23, 1)
+    toks = _tokens(cfg, 90 if name == "tile" else 23, 1)
     want = oracle_logits(cfg, w, toks)
     with torch.no_grad():
         got = model(input_ids=torch.tensor([toks], device=cuda_device)).logits[0].cpu()
     assert logits_error(got, want) < 0.06
+    # and fed as a long portion, a few tokens, then one by one: the same within 16-bit rounding
+    if name == "tile":
+        again = _run_in_portions(model, toks, [70, 5] + [1] * 15, cuda_device)
+        assert logits_error(again, want) < 0.06
 
 
 def _run_in_portions(model, toks, portions, device):
