@@ -143,7 +143,13 @@ def generate_greedy_state_graph(self, inputs=None, generation_config=None, **kwa
     B, prompt_len = input_ids.shape
     dev = input_ids.device
     with torch.cuda.device(dev):
-        g = get_state_graph(self, B, prompt_len + max_new)
+        try:
+            g = None if self.__dict__.get("_b200_state_graph_failed") else get_state_graph(self, B, prompt_len + max_new)
+        except RuntimeError as e:                            # a step that cannot be recorded: transformers' loop serves the model
+            self.__dict__["_b200_state_graph_failed"] = str(e)
+            g = None
+        if g is None:
+            return self._hf_generate(inputs, generation_config=generation_config, **kwargs)
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
         new_tokens = g.run(input_ids, attention_mask, max_new)

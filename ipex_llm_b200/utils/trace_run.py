@@ -111,6 +111,9 @@ def main(argv=None, stdin=None, stdout=None):
     a = ap.parse_args(argv)
     stdin, stdout = stdin or sys.stdin, stdout or sys.stdout
     dtype = getattr(torch, a.dtype)
+    # 16-bit matrix products accumulate in 32 bits all the way (no 16-bit reduction between the parts of a split product)
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
     if a.dtype == "float32":
         # true 32-bit: no TF32 in the matrix products
         torch.backends.cuda.matmul.allow_tf32 = False
