@@ -74,6 +74,73 @@ int mixers_poly_norm(int dtype, const void* z, long n_rows, int width, const voi
 /* out = cap * tanh(x / cap) as floats (cap <= 0: a plain conversion) */
 int mixers_soft_cap(int dtype, const void* x, long n, float cap, float* out, mixers_stream_t stream);
 
+/* ---- designs that normalise a sublayer's OUTPUT, cache a key/value latent and route tokens to experts ---- */
+
+/* x[n, :] = table[ids[n], :] * scale + pair[row(n), :] as floats (x_copy, if given, gets the same; h, if given, the same in
+ * dtype).  row(n) = (previous id * mul_prev + ids[n] * mul_cur) mod buckets; `buckets` itself for a sequence's first token
+ * (position 0); the token before a call's first token is prev[b].  pair may be null (no second table).  ids: [B, S]; padding
+ * slots (position < 0) give zeros. */
+int mixers_embed_pair(int dtype, const void* table, float scale, const void* pair, long buckets, long mul_prev, long mul_cur,
+                      const int64_t* ids, const int64_t* prev, int B, int S, int width, int slot0, const int32_t* pad, float* x,
+                      float* x_copy, void* h, mixers_stream_t stream);
+
+/* x += y / rms(y) * gain[0] * vec[:]  (gain, vec: dtype, either may be null; y: dtype, or float if y_is_float; rms over a row
+ * with eps inside the root).  With `stack` (float [streams, n_rows, width], stack_stride = n_rows * width) the new x is stored
+ * as stream `index`, and with `coef` (dtype [index + 1]) x becomes sum_{j <= index} coef[j] * stack[j].  h (may be null): x in dtype. */
+int mixers_rms_residual(int dtype, float* x, long n_rows, int width, const void* y, int y_is_float, const void* gain, const void* vec,
+                        float eps, float* stack, long stack_stride, int index, const void* coef, void* h, mixers_stream_t stream);
+
+/* out = x / rms(x) * gain[0] * vec[:]   (x float, out dtype; gain, vec may be null) */
+int mixers_rms_norm_rows(int dtype, const float* x, long n_rows, int width, const void* gain, const void* vec, float eps, void* out,
+                         mixers_stream_t stream);
+
+/* xIELU with pq = {p, q}; with a = softplus(p) and c = 1/2 + softplus(q): f(z) = a z^2 + z/2 where z is positive, c (expm1(z) - z) + z/2 elsewhere */
+int mixers_xielu(int dtype, const void* z, long n, const void* pq, void* out, mixers_stream_t stream);
+
+/* out[n, c] = silu(in[n, off_gate + c]) * in[n, off_up + c], c < cols; in: [n_rows, ld] */
+int mixers_silu_mul(int dtype, const void* in, long n_rows, int ld, int off_gate, int off_up, int cols, void* out, mixers_stream_t stream);
+
+/* out[n, c] = gelu_tanh(g[n, c]) * table[ids[n], col0 + c], c < cols */
+int mixers_gelu_table_mul(int dtype, const void* g, long n_rows, int cols, const void* table, int ld_table, int col0, const int64_t* ids,
+                          void* out, mixers_stream_t stream);
+
+/* RMS norms (plain weights q_w [q_rank], c_w [kv_rank]) of two column ranges of proj [B, S, ld]: columns off_q.. -> cq_out
+ * [B * S, q_rank]; columns off_c.. -> store [B, cap, kv_rank] at storage index held + t (zeros for padding).  dyn as above. */
+int mixers_latent_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int q_rank, const void* q_w, int off_c,
+                          int kv_rank, const void* c_w, float eps, void* cq_out, void* store, int cap, int held, int shift,
+                          const int32_t* pad, const int32_t* dyn, mixers_stream_t stream);
+
+/* Causal softmax attention of S new tokens per row.  q: head h of token n at q + n * q_ld + h * dim.  Key (value) of storage
+ * index j, row b, kv head g at k + b * k_bs + j * k_ps + g * k_hs (strides in elements).  The query at storage index c = held
+ * + t sees the keys j <= c of its row that are not padding (j + shift >= pad[b]) and, if window > 0, c - j < window.  Scores
+ * (q . k) * scale and the softmax weights are 32-bit.  out[n, out_col + h * vdim + :] in dtype (zeros for padding queries).
+ * allow_tensor_cores: 16-bit models may take the tensor-core kernel for S >= 16 (head sizes multiples of 16, <= 256). */
+int mixers_softmax_attention(int dtype, const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
+                             long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
+                             int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
+                             const int32_t* dyn, int allow_tensor_cores, mixers_stream_t stream);
+
+/* Router of a mixture of experts.  z = router h (32-bit; router [n_out, width], h [n_rows, width] in dtype), s = softmax(z) over
+ * all n_out outputs, choice = s + correction.  Outputs [g * n_out / groups, (g + 1) * n_out / groups) are group g; groups are
+ * ranked by max(choice) over their members, the `keep` first groups stay eligible (every other output is out of the running,
+ * whatever its sign), and the `top` eligible outputs of highest choice win.
+ * idx_out int32 [n_rows, top] (n_out where nothing was left to choose), w_out float [n_rows, top] = s of the chosen. */
+int mixers_grouped_router(int dtype, const void* h, long n_rows, int width, const void* router, const void* correction, int n_out,
+                          int groups, int keep, int top, int32_t* idx_out, float* w_out, mixers_stream_t stream);
+
+/* The chosen experts of a few tokens without host work.  gate_up[e] / down[e]: addresses of expert e's [2 ff, width] (gate rows,
+ * then up rows) and [width, ff] matrices in dtype.  act: scratch dtype [n_rows, top, ff].  y float [n_rows, width] =
+ * sum_k w_k * down_e (silu(gate_e h) * (up_e h)) for chosen e < n_experts, w_k * h for n_experts <= e < n_out, + shared_out
+ * (dtype [n_rows, width], may be null). */
+int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, int top, int n_experts, int n_out, const int32_t* idx,
+                     const float* wgt, const int64_t* gate_up, const int64_t* down, const void* shared_out, void* act, float* y,
+                     mixers_stream_t stream);
+
+/* y float [n_rows, width] = sum_k w[n, k] * rows[pos[n, k], :] for chosen e < n_experts, w * h[n, :] for identity experts,
+ * + shared_out; rows: dtype [*, width], the experts' outputs on rows sorted by expert. */
+int mixers_moe_combine(int dtype, const void* rows, const int32_t* pos, const int32_t* idx, const float* wgt, const void* h,
+                       const void* shared_out, long n_rows, int width, int top, int n_experts, int n_out, float* y, mixers_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

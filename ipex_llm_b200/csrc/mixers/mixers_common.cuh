@@ -28,6 +28,35 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : lo
 // log(sigmoid(z)) without cancellation on either side
 __device__ __forceinline__ float log_sigmoid_f(float z) { return z >= 0.0f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
 
+// q (32-bit, e.g. staged in shared memory) . one row of keys; 16-byte loads when the rows allow them
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ kr, int dim) {
+    float s = 0.0f;
+    if constexpr (sizeof(T) == 2) {
+        if ((dim & 7) == 0) {                                // rows start on 16-byte boundaries: eight elements a load
+            const uint4* k4 = reinterpret_cast<const uint4*>(kr);
+            const float4* q4 = reinterpret_cast<const float4*>(qs);
+            float s0 = 0.0f, s1 = 0.0f;
+            for (int d = 0; d < dim; d += 8) {
+                uint4 v = k4[d >> 3];
+                const T* e = reinterpret_cast<const T*>(&v);
+                float4 qa = q4[d >> 2], qb = q4[(d >> 2) + 1];
+                s0 += qa.x * to_f(e[0]) + qa.y * to_f(e[1]) + qa.z * to_f(e[2]) + qa.w * to_f(e[3]);
+                s1 += qb.x * to_f(e[4]) + qb.y * to_f(e[5]) + qb.z * to_f(e[6]) + qb.w * to_f(e[7]);
+            }
+            return s0 + s1;
+        }
+    }
+    for (int d = 0; d < dim; ++d) s += qs[d] * to_f(kr[d]);
+    return s;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    return v;
+}
+
 #define MIXERS_DISPATCH(dtype, ...)                                                              \
     do {                                                                                         \
         if ((dtype) == 0) { using T = float; __VA_ARGS__; }                                      \

@@ -1,0 +1,216 @@
+// Mixture-of-experts routing with groups and identity experts, and the pieces around the experts' matrix products:
+//   grouped_router: 32-bit router logits, softmax over all outputs, a correction that enters the ranking but not the
+//     weights, consecutive outputs ranked as groups first (only the leading groups stay eligible), then top-k among the
+//     eligible; weights = the winners' softmax scores;
+//   moe_small_gate_up / moe_small_down: the chosen experts of a few tokens straight from the experts' weight matrices (device
+//     tables of addresses), nothing on the host between router and result: the path of decoding and of a recorded step;
+//   moe_combine: the weighted sum of expert outputs that were computed expert by expert on sorted rows (many tokens).
+// Outputs numbered >= n_experts are identity experts: their output is the token's input itself.
+#include "mixers_common.cuh"
+#include <math.h>
+
+constexpr int ROUTER_WARPS = 4;
+
+// lowest index among the largest values of vals[0..n) that are still allowed (taken[i] == 0); one warp
+__device__ __forceinline__ int warp_argmax(const float* vals, const unsigned char* blocked, int n, int lane) {
+    float best = -INFINITY;
+    int at = -1;
+    for (int i = lane; i < n; i += 32) {
+        if (blocked[i]) continue;
+        const float v = vals[i];
+        if (at < 0 || v > best) { best = v; at = i; }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, m);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, m);
+        if (oa >= 0 && (at < 0 || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+    }
+    return at;
+}
+
+// one warp per token
+template <typename T>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32) grouped_router_kernel(
+        const T* __restrict__ h, long n_rows, int width, const T* __restrict__ router, const T* __restrict__ correction, int n_out, int groups,
+        int keep, int top, int32_t* __restrict__ idx_out, float* __restrict__ w_out) {
+    extern __shared__ float router_sh[];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_warp = 2 * n_out + groups + ((n_out + groups + 3) / 4);
+    float* score = router_sh + (long)wid * per_warp;        // softmax scores
+    float* choice = score + n_out;                          // scores + correction
+    float* gbest = choice + n_out;
+    unsigned char* blocked = reinterpret_cast<unsigned char*>(gbest + groups);      // [n_out] experts, then [groups]
+    unsigned char* gblocked = blocked + n_out;
+    const long n = blockIdx.x * (long)ROUTER_WARPS + wid;
+    if (n >= n_rows) return;
+    const T* hr = h + n * width;
+    float big = -INFINITY;
+    for (int e = 0; e < n_out; ++e) {
+        const T* r = router + (long)e * width;
+        float s = 0.0f;
+        for (int c = lane; c < width; c += 32) s += to_f(hr[c]) * to_f(r[c]);
+        s = warp_sum(s);
+        if (lane == 0) score[e] = s;
+        big = fmaxf(big, s);
+    }
+    __syncwarp();
+    float sum = 0.0f;
+    for (int e = lane; e < n_out; e += 32) sum += expf(score[e] - big);
+    sum = warp_sum(sum);
+    for (int e = lane; e < n_out; e += 32) {
+        const float s = expf(score[e] - big) / sum;
+        score[e] = s;
+        choice[e] = s + to_f(correction[e]);
+        blocked[e] = 1;
+    }
+    __syncwarp();
+    const int per = n_out / groups;
+    for (int g = lane; g < groups; g += 32) {
+        float b = -INFINITY;
+        for (int i = 0; i < per; ++i) b = fmaxf(b, choice[g * per + i]);
+        gbest[g] = b;
+        gblocked[g] = 0;
+    }
+    __syncwarp();
+    for (int r = 0; r < keep; ++r) {                        // the best groups: their members may be chosen
+        const int g = warp_argmax(gbest, gblocked, groups, lane);
+        if (g < 0) break;
+        if (lane == 0) gblocked[g] = 1;
+        for (int i = lane; i < per; i += 32) blocked[g * per + i] = 0;
+        __syncwarp();
+    }
+    for (int r = 0; r < top; ++r) {
+        const int e = warp_argmax(choice, blocked, n_out, lane);
+        if (lane == 0) {
+            idx_out[n * top + r] = e < 0 ? n_out : e;       // n_out: nothing left to choose (weight 0)
+            w_out[n * top + r] = e < 0 ? 0.0f : score[e];
+            if (e >= 0) blocked[e] = 1;
+        }
+        __syncwarp();
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __restrict__ b, int n, int lane) {
+    float s = 0.0f;
+    if constexpr (sizeof(T) == 2) {
+        if ((n & 7) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+            for (int c = lane * 8; c < n; c += 256) {
+                uint4 va = *reinterpret_cast<const uint4*>(a + c), vb = *reinterpret_cast<const uint4*>(b + c);
+                const T* ea = reinterpret_cast<const T*>(&va);
+                const T* eb = reinterpret_cast<const T*>(&vb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s += to_f(ea[i]) * to_f(eb[i]);
+            }
+            return warp_sum(s);
+        }
+    }
+    for (int c = lane; c < n; c += 32) s += to_f(a[c]) * to_f(b[c]);
+    return warp_sum(s);
+}
+
+// grid (ceil(ff / 8), n_rows * top), 8 warps a block, one warp per row of the chosen expert's gate and up matrices.
+// gate_up[e]: address of expert e's [2 ff, width] matrix (gate rows first).  act[n, k, j] = silu(gate_j . h) * (up_j . h)
+template <typename T>
+__global__ void __launch_bounds__(256) moe_small_up_kernel(const T* __restrict__ h, const int32_t* __restrict__ idx, const int64_t* __restrict__ gate_up,
+                                                           int width, int ff, int top, int n_experts, T* __restrict__ act) {
+    const int lane = threadIdx.x & 31;
+    const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long nk = blockIdx.y;
+    const int e = idx[nk];
+    if (j >= ff || e >= n_experts) return;
+    const long n = nk / top;
+    const T* w = reinterpret_cast<const T*>(gate_up[e]);
+    const T* hr = h + n * width;
+    // the products leave the matrix unit of the many-token path rounded to the model's type: the same rounding here
+    const float g = to_f(from_f<T>(warp_dot(w + (long)j * width, hr, width, lane)));
+    const float u = to_f(from_f<T>(warp_dot(w + ((long)ff + j) * width, hr, width, lane)));
+    if (lane == 0) act[nk * ff + j] = from_f<T>(silu_f(g) * u);
+}
+
+// grid (ceil(width / 8), n_rows): one warp per output column.  y[n, c] = sum_k w[n, k] * (down[e_k][c, :] . act[n, k, :])
+// (identity experts: w * h[n, c]) + shared[n, c]
+template <typename T>
+__global__ void __launch_bounds__(256) moe_small_down_kernel(const T* __restrict__ act, const int32_t* __restrict__ idx, const float* __restrict__ wgt,
+                                                             const int64_t* __restrict__ down, const T* __restrict__ h, const T* __restrict__ shared_out,
+                                                             int width, int ff, int top, int n_experts, int n_out, float* __restrict__ y) {
+    const int lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long n = blockIdx.y;
+    if (c >= width) return;
+    float sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        const int e = idx[n * top + k];
+        const float w = wgt[n * top + k];
+        if (e < n_experts) {
+            const T* wd = reinterpret_cast<const T*>(down[e]);
+            sum += w * to_f(from_f<T>(warp_dot(wd + (long)c * ff, act + (n * top + k) * ff, ff, lane)));
+        } else if (e < n_out) {
+            sum += w * to_f(h[n * width + c]);
+        }
+    }
+    if (shared_out) sum += to_f(shared_out[n * width + c]);
+    if (lane == 0) y[n * width + c] = sum;
+}
+
+// y[n, c] = sum_k w[n, k] * rows[pos[n, k], c] (identity experts: w * h[n, c]) + shared[n, c]
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ pos, const int32_t* __restrict__ idx,
+                                   const float* __restrict__ wgt, const T* __restrict__ h, const T* __restrict__ shared_out, long n_rows, int width,
+                                   int top, int n_experts, int n_out, float* __restrict__ y) {
+    const long total = n_rows * width;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long n = i / width;
+        const int c = (int)(i - n * width);
+        float sum = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            const int e = idx[n * top + k];
+            const float w = wgt[n * top + k];
+            if (e < n_experts) sum += w * to_f(rows[(long)pos[n * top + k] * width + c]);
+            else if (e < n_out) sum += w * to_f(h[i]);
+        }
+        if (shared_out) sum += to_f(shared_out[i]);
+        y[i] = sum;
+    }
+}
+
+extern "C" int mixers_grouped_router(int dtype, const void* h, long n_rows, int width, const void* router, const void* correction, int n_out,
+                                     int groups, int keep, int top, int32_t* idx_out, float* w_out, mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (groups < 1 || n_out % groups != 0 || keep < 1 || keep > groups || top < 1) return (int)cudaErrorInvalidValue;
+    const int per_warp = 2 * n_out + groups + ((n_out + groups + 3) / 4);
+    size_t smem = (size_t)ROUTER_WARPS * per_warp * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    unsigned blocks = (unsigned)((n_rows + ROUTER_WARPS - 1) / ROUTER_WARPS);
+    MIXERS_DISPATCH(dtype, grouped_router_kernel<T><<<blocks, ROUTER_WARPS * 32, smem, (cudaStream_t)stream>>>(
+        (const T*)h, n_rows, width, (const T*)router, (const T*)correction, n_out, groups, keep, top, idx_out, w_out));
+    return mixers_status();
+}
+
+extern "C" int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, int top, int n_experts, int n_out, const int32_t* idx,
+                                const float* wgt, const int64_t* gate_up, const int64_t* down, const void* shared_out, void* act, float* y,
+                                mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows * top > 65535 || n_rows > 65535) return (int)cudaErrorInvalidValue;
+    if (n_experts > 0 && ff > 0) {
+        dim3 g1((ff + 7) / 8, (unsigned)(n_rows * top));
+        MIXERS_DISPATCH(dtype, moe_small_up_kernel<T><<<g1, 256, 0, (cudaStream_t)stream>>>((const T*)h, idx, gate_up, width, ff, top, n_experts, (T*)act));
+    }
+    dim3 g2((width + 7) / 8, (unsigned)n_rows);
+    MIXERS_DISPATCH(dtype, moe_small_down_kernel<T><<<g2, 256, 0, (cudaStream_t)stream>>>(
+        (const T*)act, idx, wgt, down, (const T*)h, (const T*)shared_out, width, ff, top, n_experts, n_out, y));
+    return mixers_status();
+}
+
+extern "C" int mixers_moe_combine(int dtype, const void* rows, const int32_t* pos, const int32_t* idx, const float* wgt, const void* h,
+                                  const void* shared_out, long n_rows, int width, int top, int n_experts, int n_out, float* y,
+                                  mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    long total = n_rows * width;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    MIXERS_DISPATCH(dtype, moe_combine_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+        (const T*)rows, pos, idx, wgt, (const T*)h, (const T*)shared_out, n_rows, width, top, n_experts, n_out, y));
+    return mixers_status();
+}

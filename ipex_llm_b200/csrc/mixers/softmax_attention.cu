@@ -1,0 +1,397 @@
+// Causal softmax attention over keys and values that are addressed by strides, and the preparation of a latent cache.
+//   latent_prepare: RMS norm (plain weight) of two column ranges of one projection output: the query latent goes to a dense
+//     buffer, the key/value latent is appended to the cache (one vector per position, shared by all heads);
+//   softmax_attention: scores, softmax and the weighted sum of values with 32-bit scores and weights.  Keys and values are
+//     [batch, position, kv head, channel] tensors given by three strides each, so the same kernels serve keys / values
+//     expanded from the latent (one row per head) and the latent cache itself read as one shared key = value head of
+//     kv_rank channels (the "absorbed" form: the query carries the key expansion, the value expansion follows the sum).
+//   An optional window limits how far back a query looks (0 = every earlier position).
+#include "mixers_common.cuh"
+#include <math.h>
+
+// one warp per (token, segment): segment 0 = query latent, 1 = key/value latent
+template <typename T>
+__global__ void latent_prepare_kernel(const T* __restrict__ proj, int B, int S, int ld, int off_q, int q_rank, const T* __restrict__ q_w,
+                                      int off_c, int kv_rank, const T* __restrict__ c_w, float eps, T* __restrict__ cq_out,
+                                      T* __restrict__ store, int cap, int held, int shift, const int32_t* __restrict__ pad,
+                                      const int32_t* __restrict__ dyn) {
+    if (dyn) held = dyn[0];
+    long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= 2L * B * S) return;
+    const long n = warp >> 1;
+    const int seg = (int)(warp & 1);
+    const int b = (int)(n / S), t = (int)(n - (long)b * S);
+    const bool real = held + t + shift - pad[b] >= 0;       // padding slots hold zeros
+    const int width = seg ? kv_rank : q_rank;
+    if (width == 0) return;
+    const T* src = proj + n * (long)ld + (seg ? off_c : off_q);
+    const T* w = seg ? c_w : q_w;
+    T* dst = seg ? store + ((long)b * cap + held + t) * kv_rank : cq_out + n * (long)q_rank;
+    float ss = 0.0f;
+    for (int c = lane; c < width; c += 32) { float v = to_f(src[c]); ss += v * v; }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int c = lane; c < width; c += 32) dst[c] = from_f<T>(real ? to_f(src[c]) * inv * to_f(w[c]) : 0.0f);
+}
+
+// ---- the general kernel: any sizes and strides, any dtype, 32-bit arithmetic throughout (float32 models, decoding, short
+// portions).  A block of SA_WARPS warps per (token, query head); the warps take the visible keys in turns of 32, each with its
+// own running maximum, sum and weighted values; the warps' partial results are merged in shared memory in warp order.
+constexpr int SA_WARPS = 8;
+constexpr int SA_VCOLS = 16;                                // value columns a lane owns per pass (columns lane, lane + 32, ...)
+
+template <typename T>
+__device__ __forceinline__ float dot_strided(const float* __restrict__ qs, const T* __restrict__ kr, int dim, bool aligned) {
+    if (aligned) return dot_row(qs, kr, dim);
+    float s = 0.0f;
+    for (int d = 0; d < dim; ++d) s += qs[d] * to_f(kr[d]);
+    return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
+        const T* __restrict__ q, long q_ld, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
+        long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
+        float scale, T* __restrict__ out, long ld_out, int out_col, const int32_t* __restrict__ dyn, int aligned) {
+    extern __shared__ __align__(16) float sa_sh[];          // q [dim rounded up to 4], warp maxima, warp sums, partial values
+    const int dim4 = (dim + 3) & ~3;
+    float* qs = sa_sh;
+    float* wm = sa_sh + dim4;
+    float* wl = wm + SA_WARPS;
+    float* part = wl + SA_WARPS;                            // [SA_WARPS][SA_VCOLS * 32]
+    if (dyn) held = dyn[0];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long item = blockIdx.x;
+    const long n = item / heads;
+    const int h = (int)(item - n * heads);
+    const int b = (int)(n / S), t = (int)(n - (long)b * S);
+    const int g = h / (heads / kv_heads);
+    const int c = held + t;                                 // the query's own storage index
+    T* dst = out + n * ld_out + out_col + (long)h * vdim;
+    const int first_real = pad[b] - shift;
+    if (c < first_real) {
+        for (int col = threadIdx.x; col < vdim; col += blockDim.x) dst[col] = from_f<T>(0.0f);
+        return;
+    }
+    int lo = window > 0 ? c - window + 1 : 0;
+    if (lo < first_real) lo = first_real;
+    if (lo < 0) lo = 0;
+    const T* qsrc = q + n * q_ld + (long)h * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) qs[d] = to_f(qsrc[d]);
+    __syncthreads();
+    const T* kbase = k + b * k_bs + g * k_hs;
+    const T* vbase = v + b * v_bs + g * v_hs;
+    for (int col0 = 0; col0 < vdim; col0 += SA_VCOLS * 32) {
+        float m = -INFINITY, l = 0.0f;
+        float acc[SA_VCOLS];
+#pragma unroll
+        for (int i = 0; i < SA_VCOLS; ++i) acc[i] = 0.0f;
+        for (int j0 = lo + 32 * wid; j0 <= c; j0 += 32 * SA_WARPS) {
+            const int j = j0 + lane;
+            const float s = j <= c ? dot_strided(qs, kbase + j * k_ps, dim, aligned != 0) * scale : -INFINITY;
+            const float m_new = fmaxf(m, warp_max(s));      // finite: key j0 is visible
+            const float corr = expf(m - m_new);             // 0 on the first turn (m = -inf)
+            const float p = j <= c ? expf(s - m_new) : 0.0f;
+            l = l * corr + warp_sum(p);
+            m = m_new;
+#pragma unroll
+            for (int i = 0; i < SA_VCOLS; ++i) acc[i] *= corr;
+            const int nk = c - j0 + 1 < 32 ? c - j0 + 1 : 32;
+            for (int jj = 0; jj < nk; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const T* vr = vbase + (j0 + jj) * v_ps + col0;
+#pragma unroll
+                for (int i = 0; i < SA_VCOLS; ++i) {
+                    const int col = lane + 32 * i;
+                    if (col0 + col < vdim) acc[i] += pj * to_f(vr[col]);
+                }
+            }
+        }
+        if (lane == 0) { wm[wid] = m; wl[wid] = l; }
+#pragma unroll
+        for (int i = 0; i < SA_VCOLS; ++i) part[(wid * SA_VCOLS + i) * 32 + lane] = acc[i];
+        __syncthreads();
+        float big = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < SA_WARPS; ++w) big = fmaxf(big, wm[w]);
+        float f[SA_WARPS], total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SA_WARPS; ++w) { f[w] = wm[w] == -INFINITY ? 0.0f : expf(wm[w] - big); total += wl[w] * f[w]; }
+        for (int e = threadIdx.x; e < SA_VCOLS * 32; e += blockDim.x) {
+            const int col = col0 + e;                       // e = i * 32 + lane, column = col0 + lane + 32 i
+            if (col < vdim) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < SA_WARPS; ++w) sum += part[w * SA_VCOLS * 32 + e] * f[w];
+                dst[col] = from_f<T>(sum / total);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---- many new tokens of a 16-bit model: both products on the tensor cores (mma.sync m16n8k16, 32-bit accumulators).
+// A block of 4 warps takes 64 consecutive query tokens of one head (16 rows a warp, queries as A fragments in registers) and
+// walks the keys they can see 32 at a time: K and V tiles staged in shared memory (rows padded by 16 bytes: conflict-free
+// fragment reads and transposing ldmatrix), S = Q K^T, then per row the running maximum and sum of the softmax in 32-bit
+// floats, P = exp(S - max) with everything a row cannot see set to zero, O = O * correction + P V.  P goes to the tensor cores
+// as the sum of two 16-bit numbers (its rounding and the rounding's remainder): the weights keep ~16 bits of mantissa.
+template <typename T> struct SaMma;
+template <> struct SaMma<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+};
+template <> struct SaMma<__half> {
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+};
+
+constexpr int SA_ROWS = 64, SA_KEYS = 32;
+
+template <typename T, int KDMAX, int NDMAX>                // dim <= 16 KDMAX, vdim <= 8 NDMAX; both multiples of 16
+__global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
+        const T* __restrict__ q, long q_ld, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
+        long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
+        float scale, T* __restrict__ out, long ld_out, int out_col) {
+    extern __shared__ __align__(16) unsigned char sa_tc_sh[];
+    const int kstride = dim + 8, vstride = vdim + 8;        // elements
+    T* Ks = reinterpret_cast<T*>(sa_tc_sh);                 // [SA_KEYS][kstride]
+    T* Vs = Ks + SA_KEYS * kstride;                         // [SA_KEYS][vstride]
+    // the last query tiles first: they see the most keys
+    const int b = blockIdx.z, h = blockIdx.y, t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * SA_ROWS;
+    const int g = h / (heads / kv_heads);
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31, gr = lane >> 2, tq = lane & 3;
+    const int kdn = dim >> 4, ndn = vdim >> 3;
+    const int first_real = pad[b] - shift;
+    const int t_last = (t0 + SA_ROWS - 1 < S - 1) ? t0 + SA_ROWS - 1 : S - 1;
+    const int c_hi = held + t_last;                         // newest key this block can see
+    int j_start = window > 0 ? held + t0 - window + 1 : 0;
+    if (j_start < first_real) j_start = first_real;
+    if (j_start < 0) j_start = 0;
+    const int r0 = t0 + wid * 16;                           // this warp's rows
+    const int tr[2] = {r0 + gr, r0 + gr + 8};
+    int row_c[2], row_lo[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        row_c[i] = held + tr[i];
+        int lo = window > 0 ? row_c[i] - window + 1 : 0;
+        if (lo < first_real) lo = first_real;
+        if (lo < 0) lo = 0;
+        row_lo[i] = lo;
+        if (tr[i] >= S || row_c[i] < first_real) { row_c[i] = -1; row_lo[i] = 0; }      // nothing visible
+    }
+    const int warp_hi = held + ((r0 + 15 < S - 1) ? r0 + 15 : S - 1);
+    const int warp_lo = window > 0 ? held + r0 - window + 1 : 0;
+    uint32_t qa[KDMAX][4];
+#pragma unroll
+    for (int kd = 0; kd < KDMAX; ++kd) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qa[kd][i] = 0u;
+        if (kd < kdn) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (tr[i] < S) {
+                    const T* src = q + ((long)b * S + tr[i]) * q_ld + (long)h * dim + kd * 16 + 2 * tq;
+                    qa[kd][i] = *reinterpret_cast<const uint32_t*>(src);
+                    qa[kd][2 + i] = *reinterpret_cast<const uint32_t*>(src + 8);
+                }
+            }
+        }
+    }
+    float oacc[NDMAX][4];
+#pragma unroll
+    for (int nd = 0; nd < NDMAX; ++nd)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) oacc[nd][i] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};      // l: this lane's share of the row's sum
+    const T* kbase = k + b * k_bs + g * k_hs;
+    const T* vbase = v + b * v_bs + g * v_hs;
+    const int kchunks = dim >> 3, vchunks = vdim >> 3;      // 16-byte pieces per row
+
+    for (int jt = j_start; jt <= c_hi; jt += SA_KEYS) {
+        __syncthreads();                                    // the previous tile has been consumed
+        for (int id = tid; id < SA_KEYS * kchunks; id += 128) {
+            int r = id / kchunks, cch = id - r * kchunks;
+            int j = jt + r <= c_hi ? jt + r : c_hi;         // rows past the end repeat the last one (their weights are zero)
+            *reinterpret_cast<uint4*>(Ks + r * kstride + cch * 8) = *reinterpret_cast<const uint4*>(kbase + j * k_ps + cch * 8);
+        }
+        for (int id = tid; id < SA_KEYS * vchunks; id += 128) {
+            int r = id / vchunks, cch = id - r * vchunks;
+            int j = jt + r <= c_hi ? jt + r : c_hi;
+            *reinterpret_cast<uint4*>(Vs + r * vstride + cch * 8) = *reinterpret_cast<const uint4*>(vbase + j * v_ps + cch * 8);
+        }
+        __syncthreads();
+        if (jt > warp_hi || jt + SA_KEYS - 1 < warp_lo) continue;        // no row of this warp sees the tile
+        float sc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[nt][i] = 0.0f;
+            const T* krow = Ks + (nt * 8 + gr) * kstride + 2 * tq;
+#pragma unroll
+            for (int kd = 0; kd < KDMAX; ++kd) {
+                if (kd < kdn) {
+                    uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + kd * 16);
+                    uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + kd * 16 + 8);
+                    SaMma<T>::mma(sc[nt], qa[kd], b0, b1);
+                }
+            }
+        }
+        // scores -> masked, scaled; the rows' new maxima
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int j = jt + nt * 8 + 2 * tq + (i & 1);
+                const int r = i >> 1;
+                const float s = (j >= row_lo[r] && j <= row_c[r]) ? sc[nt][i] * scale : -INFINITY;
+                sc[nt][i] = s;
+                tmax[r] = fmaxf(tmax[r], s);
+            }
+        }
+        float corr[2], m_new[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+            m_new[r] = fmaxf(m_run[r], tmax[r]);
+            corr[r] = m_new[r] == -INFINITY ? 1.0f : __expf(m_run[r] - m_new[r]);
+            m_run[r] = m_new[r];
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int nd = 0; nd < NDMAX; ++nd) {
+            oacc[nd][0] *= corr[0]; oacc[nd][1] *= corr[0];
+            oacc[nd][2] *= corr[1]; oacc[nd][3] *= corr[1];
+        }
+        uint32_t ph[2][4], pl[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = i >> 1;
+                p[i] = sc[nt][i] == -INFINITY ? 0.0f : __expf(sc[nt][i] - m_new[r]);
+                l_run[r] += p[i];
+            }
+            const int ks = nt >> 1, half = nt & 1;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                uint32_t hi = SaMma<T>::pack(p[2 * r], p[2 * r + 1]);
+                float2 back = SaMma<T>::unpack(hi);
+                ph[ks][2 * half + r] = hi;
+                pl[ks][2 * half + r] = SaMma<T>::pack(p[2 * r] - back.x, p[2 * r + 1] - back.y);
+            }
+        }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+            for (int np = 0; np < NDMAX / 2; ++np) {
+                if (2 * np < ndn) {
+                    uint32_t v0, v1, v2, v3;
+                    const T* vaddr = Vs + (ks * 16 + (lane & 15)) * vstride + np * 16 + ((lane >> 4) << 3);
+                    uint32_t sa = (uint32_t)__cvta_generic_to_shared(vaddr);
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                                 : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(sa));
+                    SaMma<T>::mma(oacc[2 * np], ph[ks], v0, v1);
+                    SaMma<T>::mma(oacc[2 * np], pl[ks], v0, v1);
+                    SaMma<T>::mma(oacc[2 * np + 1], ph[ks], v2, v3);
+                    SaMma<T>::mma(oacc[2 * np + 1], pl[ks], v2, v3);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = l_run[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        if (tr[i] < S) {
+            T* dst = out + ((long)b * S + tr[i]) * ld_out + out_col + (long)h * vdim + 2 * tq;
+#pragma unroll
+            for (int nd = 0; nd < NDMAX; ++nd) {
+                if (nd < ndn) {
+                    dst[nd * 8] = from_f<T>(oacc[nd][2 * i] * inv);
+                    dst[nd * 8 + 1] = from_f<T>(oacc[nd][2 * i + 1] * inv);
+                }
+            }
+        }
+    }
+}
+
+#define SA_TC_PARAMS const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs, \
+    int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* pad, int window, float scale, void* out,     \
+    long ld_out, int out_col, cudaStream_t stream
+#define SA_TC_ARGS q, q_ld, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, scale, out, \
+    ld_out, out_col, stream
+
+template <typename T, int KDMAX, int NDMAX>
+static int launch_softmax_tc(SA_TC_PARAMS) {
+    size_t smem = (size_t)SA_KEYS * (dim + 8 + vdim + 8) * sizeof(T);
+    dim3 grid((S + SA_ROWS - 1) / SA_ROWS, heads, B);
+    softmax_attention_tc_kernel<T, KDMAX, NDMAX><<<grid, 128, smem, stream>>>(
+        (const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
+        scale, (T*)out, ld_out, out_col);
+    return mixers_status();
+}
+
+template <typename T>
+static int softmax_tc(SA_TC_PARAMS) {
+    if (dim <= 64 && vdim <= 64) return launch_softmax_tc<T, 4, 8>(SA_TC_ARGS);
+    if (dim <= 128 && vdim <= 128) return launch_softmax_tc<T, 8, 16>(SA_TC_ARGS);
+    return launch_softmax_tc<T, 16, 32>(SA_TC_ARGS);
+}
+
+extern "C" int mixers_latent_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int q_rank, const void* q_w, int off_c,
+                                     int kv_rank, const void* c_w, float eps, void* cq_out, void* store, int cap, int held, int shift,
+                                     const int32_t* pad, const int32_t* dyn, mixers_stream_t stream) {
+    if (B <= 0 || S <= 0) return 0;
+    if (held + S > cap) return (int)cudaErrorInvalidValue;
+    long warps = 2L * B * S;
+    int blocks = (int)((warps + 3) / 4);
+    MIXERS_DISPATCH(dtype, latent_prepare_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+        (const T*)proj, B, S, ld, off_q, q_rank, (const T*)q_w, off_c, kv_rank, (const T*)c_w, eps, (T*)cq_out, (T*)store, cap, held, shift, pad, dyn));
+    return mixers_status();
+}
+
+extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
+                                        long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
+                                        int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
+                                        const int32_t* dyn, int allow_tensor_cores, mixers_stream_t stream_) {
+    if (B <= 0 || S <= 0) return 0;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int dim4 = (dim + 3) & ~3;
+    size_t smem = ((size_t)dim4 + 2 * SA_WARPS + SA_WARPS * SA_VCOLS * 32) * sizeof(float);
+    if (window < 0 || kv_heads < 1 || heads % kv_heads != 0 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const size_t esz = dtype == 0 ? 4 : 2;
+    auto mult8 = [](long s) { return (s & 7) == 0; };
+    const bool rows16 = esz == 2 && mult8(k_bs) && mult8(k_ps) && mult8(k_hs) && mult8(v_bs) && mult8(v_ps) && mult8(v_hs) &&
+                        ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && (dim & 7) == 0;
+    if (allow_tensor_cores && dtype != 0 && !dyn && S >= 16 && rows16 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 256 && vdim <= 256 &&
+        (q_ld & 1) == 0 && ((uintptr_t)q & 3) == 0 && (ld_out & 1) == 0 && (out_col & 1) == 0) {
+        if (dtype == 1) return softmax_tc<__nv_bfloat16>(SA_TC_ARGS);
+        return softmax_tc<__half>(SA_TC_ARGS);
+    }
+    long items = (long)B * S * heads;
+    MIXERS_DISPATCH(dtype, softmax_attention_kernel<T><<<(unsigned)items, SA_WARPS * 32, smem, stream>>>(
+        (const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
+        scale, (T*)out, ld_out, out_col, dyn, rows16 ? 1 : 0));
+    return mixers_status();
+}

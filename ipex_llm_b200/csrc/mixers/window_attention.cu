@@ -66,28 +66,6 @@ constexpr int ATT_WARPS = 8;
 constexpr int VCOLS = 8;
 
 template <typename T>
-__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ kr, int dim) {
-    float s = 0.0f;
-    if constexpr (sizeof(T) == 2) {
-        if ((dim & 7) == 0) {                                // rows start on 16-byte boundaries: eight elements a load
-            const uint4* k4 = reinterpret_cast<const uint4*>(kr);
-            const float4* q4 = reinterpret_cast<const float4*>(qs);
-            float s0 = 0.0f, s1 = 0.0f;
-            for (int d = 0; d < dim; d += 8) {
-                uint4 v = k4[d >> 3];
-                const T* e = reinterpret_cast<const T*>(&v);
-                float4 qa = q4[d >> 2], qb = q4[(d >> 2) + 1];
-                s0 += qa.x * to_f(e[0]) + qa.y * to_f(e[1]) + qa.z * to_f(e[2]) + qa.w * to_f(e[3]);
-                s1 += qb.x * to_f(e[4]) + qb.y * to_f(e[5]) + qb.z * to_f(e[6]) + qb.w * to_f(e[7]);
-            }
-            return s0 + s1;
-        }
-    }
-    for (int d = 0; d < dim; ++d) s += qs[d] * to_f(kr[d]);
-    return s;
-}
-
-template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) sigmoid_window_attention_kernel(
         const float* __restrict__ q, const T* __restrict__ k_store, const T* __restrict__ v_store, int B, int S, int heads, int kv_heads, int dim,
         int vdim, int cap, int held, int shift, const int32_t* __restrict__ pad, int window, float scale, const T* __restrict__ head_bias,

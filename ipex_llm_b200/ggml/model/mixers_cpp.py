@@ -1,6 +1,6 @@
 """ctypes binding of libb200mixers.so (include/b200_mixers.h): the kernels of decoder layers that are not softmax attention.
 
-The library is built on first use when it is missing or older than its sources (``build_native.build_mixers``: three small
+The library is built on first use when it is missing or older than its sources (``build_native.build_mixers``: a handful of small
 files, seconds) -- a fresh checkout serves such a model without building the low-bit library.  There is no CPU or PyTorch
 fallback: without the library, or on tensors that are not on a CUDA device, the calls raise.
 """
@@ -35,6 +35,22 @@ _SIGNATURES = {
                               _c_float, _c_ptr],
     "mixers_poly_norm": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_float, _c_ptr, _c_ptr],
     "mixers_soft_cap": [_c_int, _c_ptr, _c_long, _c_float, _c_ptr, _c_ptr],
+    "mixers_embed_pair": [_c_int, _c_ptr, _c_float, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                          _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_rms_residual": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr,
+                            _c_ptr],
+    "mixers_rms_norm_rows": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr],
+    "mixers_xielu": [_c_int, _c_ptr, _c_long, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_silu_mul": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "mixers_gelu_table_mul": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_latent_prepare": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_ptr,
+                              _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_softmax_attention": [_c_int, _c_ptr, _c_long, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long] + [_c_int] * 8
+                                + [_c_ptr, _c_int, _c_float, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr],
+    "mixers_grouped_router": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_moe_small": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                         _c_ptr],
+    "mixers_moe_combine": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
 }
 
 

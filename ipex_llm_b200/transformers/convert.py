@@ -165,6 +165,10 @@ def _optimize_pre(model, qtype=None):
         import functools
         from ipex_llm_b200.transformers.models.zafepel import merge_projections
         model.apply(functools.partial(merge_projections, row_multiple=128 if qtype is not None else 0))
+    elif model_type == "serotar":
+        # the query-latent and key/value-latent projections read the same input -> one in_proj
+        from ipex_llm_b200.transformers.models.serotar import merge_projections
+        model.apply(merge_projections)
     return model
 
 
@@ -196,7 +200,7 @@ def _optimize_post(model):
         convert_forward(model, module.MixtralRMSNorm, rms_norm_forward)
         convert_forward(model, module.MixtralModel, mixtral_model_forward)
         convert_forward(model, module.MixtralAttention, mixtral_attention_forward)
-    elif model_type == "zafepel":
+    elif model_type in ("zafepel", "serotar"):
         # this package's own model class: its forwards already call the fused operators and pick the state cache;
         # the recorded decode step for such a cache goes behind generate()
         from ipex_llm_b200.transformers.state_decode_graph import install_state_generate

@@ -416,6 +416,58 @@ class WindowKVLayer(NormalKVLayer):
                 setattr(self, name, fresh)
 
 
+class LatentKVLayer:
+    """One vector per position from which every head's keys and values are expanded (a key/value latent): storage
+    [B, capacity, rank], grown in blocks like ``NormalKVLayer``.  The kernel that normalises the latent writes it into
+    ``slots(n)`` -- the storage with room for ``n`` more positions -- and ``commit(n)`` moves the length.  Nothing is ever
+    dropped: every earlier position stays visible."""
+
+    def __init__(self, reserve: int = 0):
+        self.reserve = int(reserve)
+        self.store = None                 # [B, capacity, rank]
+        self.length = 0
+        self.length_dev = None            # int32 [1] on the device: the positions held, for a step replayed from a CUDA graph
+
+    def slots(self, batch, rank, n_new, dtype, device):
+        """(storage [B, capacity, rank] with room for n_new more positions, positions held)"""
+        need = self.length + n_new
+        if self.store is None or self.store.shape[1] < need:
+            cap = max(need, self.reserve) + KV_ALLOC_BLOCK_LENGTH
+            fresh = torch.empty(batch, cap, rank, dtype=dtype, device=device)
+            if self.store is not None and self.length:
+                fresh[:, :self.length].copy_(self.store[:, :self.length])
+            self.store = fresh
+        invalidInputError(self.store.shape[0] == batch and self.store.shape[2] == rank and self.store.dtype == dtype,
+                          "the latent cache was started with another batch size, rank or dtype")
+        return self.store, self.length
+
+    def commit(self, n_new):
+        self.length += n_new
+
+    def held(self):
+        """the positions held, as a view [B, length, rank]"""
+        return self.store[:, :self.length]
+
+    def get_seq_length(self):
+        return self.length
+
+    def capacity(self):
+        return 0 if self.store is None else self.store.shape[1]
+
+    def clear(self):
+        """forget the positions held, keep the storage (and its address)"""
+        self.length = 0
+
+    def trim(self):
+        pass
+
+    def select(self, index):
+        if self.store is not None:
+            fresh = torch.empty((index.shape[0],) + tuple(self.store.shape[1:]), dtype=self.store.dtype, device=self.store.device)
+            fresh[:, :self.length].copy_(self.store.index_select(0, index)[:, :self.length])
+            self.store = fresh
+
+
 class RecurrentStateLayer:
     """What a linear recurrence carries from token to token: the matrix state [B, H, D, Dv] in 32-bit floats and, where a
     short convolution precedes it, the last ``taps - 1`` inputs of every channel [B, taps - 1, C].  Over several new tokens the
@@ -452,10 +504,11 @@ class RecurrentStateLayer:
 
 class MixerStateLayer:
     """the state of one RUN of a layer (a layer that a model runs several times keeps one of these per run): a window of
-    keys and values, a recurrent state, or both for a layer that runs the two side by side"""
+    keys and values, a key/value latent, a recurrent state, or attention and recurrence for a layer that runs the two side by
+    side"""
 
-    def __init__(self, window=None, reserve=0):
-        self.kv = WindowKVLayer(reserve, window) if window is not None else None
+    def __init__(self, window=None, reserve=0, latent=False):
+        self.kv = LatentKVLayer(reserve) if latent else (WindowKVLayer(reserve, window) if window is not None else None)
         self.rec = RecurrentStateLayer()
 
     def select(self, index):
@@ -480,13 +533,20 @@ class DynamicStateCache(Cache):
         self.seen = 0
         self.pad = None                                  # int32 [B] on the model's device
         self.frozen = False                              # storage stays where it is: no trimming (a recorded step holds its addresses)
+        self.last_token = None                           # int64 [B]: see previous_tokens
 
-    def run_state(self, run_idx, window=None):
+    def run_state(self, run_idx, window=None, latent=False):
         while len(self.layers) <= run_idx:
             self.layers.append(None)
         if self.layers[run_idx] is None:
-            self.layers[run_idx] = MixerStateLayer(window, self.reserve)
+            self.layers[run_idx] = MixerStateLayer(window, self.reserve, latent)
         return self.layers[run_idx]
+
+    def previous_tokens(self, batch, device):
+        """int64 [B]: the last token every row was fed (what an embedding of token pairs needs of the past)"""
+        if self.last_token is None:
+            self.last_token = torch.zeros(batch, dtype=torch.int64, device=device)
+        return self.last_token
 
     def start(self, attention_mask, batch, length, device):
         """the first call of a batch: left padding from the mask (ones after zeros in every row)"""
@@ -535,6 +595,8 @@ class DynamicStateCache(Cache):
     def batch_select_indices(self, indices):
         indices = torch.as_tensor(indices, dtype=torch.int64, device=self.pad.device)
         self.pad = self.pad.index_select(0, indices).contiguous()
+        if self.last_token is not None:
+            self.last_token = self.last_token.index_select(0, indices).contiguous()
         for l in self.layers:
             if l is not None:
                 l.select(indices)
@@ -550,4 +612,4 @@ class DynamicStateCache(Cache):
         invalidInputError(False, "a recurrent state cannot be rolled back to an earlier length")
 
     def reset(self):
-        self.layers, self.seen, self.pad = [], 0, None
+        self.layers, self.seen, self.pad, self.last_token = [], 0, None, None

@@ -133,3 +133,136 @@ def soft_cap(x, cap):
     native.call("mixers_soft_cap", native.dtype_code(x.dtype), native.ptr(x), x.numel(), float(cap) if cap else 0.0, native.ptr(out),
                 native.stream(x.device))
     return out
+
+
+# ------------------------------------------------------------------ output-normalised residual stream, latent attention, routed experts
+def embed_pair(table, scale, pair, buckets, mul_prev, mul_cur, ids, prev, slot0, pad, out_dtype, x_copy=None):
+    """fp32 x [N, W] = table[id] * scale + pair[row]; also returns x in ``out_dtype``.  ids [B, S] int64, prev [B] int64 (the token
+    before each row's first new one); ``x_copy``: a second fp32 [N, W] destination (the first of the kept streams)."""
+    B, S = ids.shape
+    ids = _c(ids)
+    w = table.shape[1]
+    invalidInputError(table.is_contiguous() and (pair is None or (pair.is_contiguous() and pair.shape[1] == w and pair.shape[0] > buckets)),
+                      "embed_pair: unexpected layout")
+    x = torch.empty(B * S, w, dtype=torch.float32, device=table.device)
+    h = torch.empty(B * S, w, dtype=out_dtype, device=table.device)
+    native.call("mixers_embed_pair", native.dtype_code(table.dtype), native.ptr(table), float(scale), native.ptr(pair), int(buckets), int(mul_prev),
+                int(mul_cur), native.ptr(ids), native.ptr(prev), B, S, w, int(slot0), native.ptr(pad), native.ptr(x), native.ptr(x_copy),
+                native.ptr(h), native.stream(x.device))
+    return x, h
+
+
+def rms_residual(x, y, gain, vec, eps, out_dtype, stack=None, index=0, coef=None, want_h=True):
+    """x += y / rms(y) * gain * vec in place (x fp32 [N, W]); with ``stack`` [streams, N, W] the new x is kept as stream ``index``
+    and, with ``coef`` [index + 1], replaced by the coefficient-weighted sum of streams 0..index.  Returns x in ``out_dtype``."""
+    n, w = x.shape
+    y = _c(y)
+    invalidInputError(x.dtype == torch.float32 and x.is_contiguous() and y.shape == x.shape and y.dtype in (out_dtype, torch.float32),
+                      "rms_residual: x is a contiguous fp32 [N, W], y the model's dtype or fp32")
+    invalidInputError(stack is None or (stack.dtype == torch.float32 and stack.is_contiguous() and stack.shape[1:] == x.shape and index < stack.shape[0]),
+                      "rms_residual: the kept streams are a contiguous fp32 [streams, N, W]")
+    invalidInputError(coef is None or (stack is not None and coef.numel() == index + 1), "rms_residual: one coefficient per kept stream")
+    h = torch.empty(n, w, dtype=out_dtype, device=x.device) if want_h else None
+    native.call("mixers_rms_residual", native.dtype_code(out_dtype), native.ptr(x), n, w, native.ptr(y), int(y.dtype == torch.float32 and out_dtype != torch.float32),
+                native.ptr(gain), native.ptr(vec), float(eps), native.ptr(stack), n * w, int(index), native.ptr(coef), native.ptr(h),
+                native.stream(x.device))
+    return h
+
+
+def rms_norm_rows(x, gain, vec, eps, out_dtype):
+    x = _c(x)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    native.call("mixers_rms_norm_rows", native.dtype_code(out_dtype), native.ptr(x), x.numel() // x.shape[-1], x.shape[-1], native.ptr(gain),
+                native.ptr(vec), float(eps), native.ptr(out), native.stream(x.device))
+    return out
+
+
+def xielu(z, pq):
+    z = _c(z)
+    out = torch.empty_like(z)
+    native.call("mixers_xielu", native.dtype_code(z.dtype), native.ptr(z), z.numel(), native.ptr(pq), native.ptr(out), native.stream(z.device))
+    return out
+
+
+def silu_mul(gate_up, cols):
+    """silu(first ``cols`` columns) * the next ``cols`` columns"""
+    gate_up = _c(gate_up)
+    n = gate_up.numel() // gate_up.shape[-1]
+    out = torch.empty(n, cols, dtype=gate_up.dtype, device=gate_up.device)
+    if n:
+        native.call("mixers_silu_mul", native.dtype_code(gate_up.dtype), native.ptr(gate_up), n, gate_up.shape[-1], 0, cols, cols, native.ptr(out),
+                    native.stream(out.device))
+    return out
+
+
+def gelu_table_mul(g, table, col0, ids):
+    """gelu_tanh(g [N, C]) * table[ids, col0 : col0 + C]"""
+    g, ids = _c(g), _c(ids)
+    out = torch.empty_like(g)
+    native.call("mixers_gelu_table_mul", native.dtype_code(g.dtype), native.ptr(g), g.shape[0], g.shape[1], native.ptr(table), table.shape[1], int(col0),
+                native.ptr(ids), native.ptr(out), native.stream(g.device))
+    return out
+
+
+def latent_prepare(proj, off_q, q_rank, q_w, off_c, kv_rank, c_w, eps, store, held, shift, pad, dyn=None):
+    """the normalised query latent [B * S, q_rank]; the normalised key/value latent goes into ``store`` [B, cap, kv_rank]"""
+    B, S, P = proj.shape
+    invalidInputError(proj.is_contiguous() and store.is_contiguous() and store.dtype == proj.dtype and store.shape[0] == B
+                      and store.shape[2] == kv_rank, "latent_prepare: unexpected layout")
+    cq = torch.empty(B * S, q_rank, dtype=proj.dtype, device=proj.device)
+    native.call("mixers_latent_prepare", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, off_q, q_rank, native.ptr(q_w), off_c, kv_rank,
+                native.ptr(c_w), float(eps), native.ptr(cq), native.ptr(store), store.shape[1], int(held), int(shift), native.ptr(pad), native.ptr(dyn),
+                native.stream(proj.device))
+    return cq
+
+
+def softmax_attention(q, k, v, B, S, heads, held, shift, pad, window, scale, out=None, out_col=0, dyn=None, tensor_cores=True):
+    """q [B * S, heads * dim] (rows may be strided); k [B, L, kv_heads, dim], v [B, L, kv_heads, vdim] views (any strides with a
+    unit last one); returns out [B * S, heads * vdim] in q's dtype"""
+    kv_heads, dim, vdim = k.shape[2], k.shape[3], v.shape[3]
+    invalidInputError(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and q.shape[-1] == heads * dim and k.dtype == q.dtype
+                      and v.dtype == q.dtype and v.shape[2] == kv_heads and (dyn is not None or (k.shape[1] >= held + S and v.shape[1] >= held + S)),
+                      "softmax_attention: unexpected layout")
+    if out is None:
+        out = torch.empty(B * S, heads * vdim, dtype=q.dtype, device=q.device)
+    native.call("mixers_softmax_attention", native.dtype_code(q.dtype), native.ptr(q), q.stride(0), native.ptr(k), k.stride(0), k.stride(1), k.stride(2),
+                native.ptr(v), v.stride(0), v.stride(1), v.stride(2), B, S, heads, kv_heads, dim, vdim, int(held), int(shift), native.ptr(pad),
+                int(window), float(scale), native.ptr(out), out.stride(0), int(out_col), native.ptr(dyn), int(bool(tensor_cores)),
+                native.stream(q.device))
+    return out
+
+
+def grouped_router(h, router, correction, groups, keep, top):
+    """(chosen outputs int32 [N, top], their softmax scores fp32 [N, top])"""
+    h = _c(h)
+    n, w = h.shape
+    invalidInputError(router.is_contiguous() and router.shape[1] == w and router.dtype == h.dtype and correction.dtype == h.dtype
+                      and correction.numel() == router.shape[0], "grouped_router: unexpected layout")
+    idx = torch.empty(n, top, dtype=torch.int32, device=h.device)
+    wgt = torch.empty(n, top, dtype=torch.float32, device=h.device)
+    native.call("mixers_grouped_router", native.dtype_code(h.dtype), native.ptr(h), n, w, native.ptr(router), native.ptr(correction), router.shape[0],
+                int(groups), int(keep), int(top), native.ptr(idx), native.ptr(wgt), native.stream(h.device))
+    return idx, wgt
+
+
+def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shared_out):
+    """fp32 [N, W]: the chosen experts of a few tokens through tables of the experts' weight addresses"""
+    h = _c(h)
+    n, w = h.shape
+    top = idx.shape[1]
+    act = torch.empty(max(n * top * ff, 1), dtype=h.dtype, device=h.device)
+    y = torch.empty(n, w, dtype=torch.float32, device=h.device)
+    native.call("mixers_moe_small", native.dtype_code(h.dtype), native.ptr(h), n, w, int(ff), top, int(n_experts), int(n_out), native.ptr(idx),
+                native.ptr(wgt), native.ptr(gate_up_table), native.ptr(down_table), native.ptr(shared_out), native.ptr(act), native.ptr(y),
+                native.stream(h.device))
+    return y
+
+
+def moe_combine(rows, pos, idx, wgt, h, shared_out, n_experts, n_out):
+    """fp32 [N, W]: weighted sum of the experts' outputs ``rows`` (row pos[n, k] belongs to token n's k-th choice)"""
+    h = _c(h)
+    n, w = h.shape
+    y = torch.empty(n, w, dtype=torch.float32, device=h.device)
+    native.call("mixers_moe_combine", native.dtype_code(h.dtype), native.ptr(rows), native.ptr(pos), native.ptr(idx), native.ptr(wgt), native.ptr(h),
+                native.ptr(shared_out), n, w, idx.shape[1], int(n_experts), int(n_out), native.ptr(y), native.stream(h.device))
+    return y

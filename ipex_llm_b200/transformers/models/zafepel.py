@@ -25,6 +25,7 @@ from transformers.modeling_outputs import CausalLMOutputWithPast
 from ipex_llm_b200.transformers.kv import DynamicStateCache
 from ipex_llm_b200.transformers.models import mixer_ops as ops
 from ipex_llm_b200.transformers.models.common import merge_linear, merge_linear_inputs
+from ipex_llm_b200.transformers.models.utils import read_safetensors
 from ipex_llm_b200.utils.common import invalidInputError
 
 
@@ -366,31 +367,6 @@ class ZafepelForCausalLM(PreTrainedModel, GenerationMixin):
 
 
 # ------------------------------------------------------------------ checkpoint
-def read_safetensors(path):
-    """name -> tensor from a safetensors file: an 8-byte little-endian header length, a JSON header (dtype, shape, data
-    offsets per name), then the raw little-endian data"""
-    import numpy as np
-    dtypes = {"BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F32": (torch.float32, 4), "F64": (torch.float64, 8),
-              "I32": (torch.int32, 4), "I64": (torch.int64, 8), "I16": (torch.int16, 2), "I8": (torch.int8, 1), "U8": (torch.uint8, 1)}
-    with open(path, "rb") as f:
-        n = int.from_bytes(f.read(8), "little")
-        header = json.loads(f.read(n))
-    data = np.memmap(path, dtype=np.uint8, mode="r", offset=8 + n)
-    out = {}
-    for name, meta in header.items():
-        if name == "__metadata__":
-            continue
-        dt, size = dtypes[meta["dtype"]]
-        lo, hi = meta["data_offsets"]
-        count = 1
-        for d in meta["shape"]:
-            count *= d
-        invalidInputError(hi - lo == count * size, f"tensor {name}: {hi - lo} bytes for shape {meta['shape']}")
-        raw = torch.from_numpy(np.array(data[lo:hi]))                        # a copy: the file may go away
-        out[name] = raw.view(dt).reshape(meta["shape"])
-    return out
-
-
 def checkpoint_key_map(config: ZafepelConfig):
     """the model's parameter names -> the checkpoint's tensor names (or a list of them, concatenated by rows)"""
     m = {"model.embed_tokens.weight": "embed", "lm_head.weight": "head"}

@@ -49,7 +49,7 @@ class StateDecodeGraph:
         torch.cuda.current_stream(dev).wait_stream(self.graph.stream)
 
     def _sync_lengths(self):
-        self.lengths.copy_(torch.tensor([kv.keys.shape[2] for kv in self.kvs] or [0], dtype=torch.int32))
+        self.lengths.copy_(torch.tensor([kv.get_seq_length() for kv in self.kvs] or [0], dtype=torch.int32))
 
     def _step(self):
         out = self.model(input_ids=self.ids, past_key_values=self.cache, use_cache=True, logits_to_keep=1)
