@@ -140,3 +140,109 @@ def forward(cfg, w, tokens, collect=None):
         if collect is not None:
             collect.append(x)
     return scalar_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def windowed_attention(q, k, v, scale, window=0, first=0, held=0):
+    """the general statement behind the attention kernel, by loops: q [S, H, D] are the queries of storage indices held .. held +
+    S - 1; k [L, G, D], v [L, G, Dv] with H a multiple of G; index j is visible to the query at c when first <= j <= c and
+    (window == 0 or c - j < window).  Queries in front of ``first`` give zeros."""
+    S, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(S, H, v.shape[2], dtype=q.dtype)
+    for t in range(S):
+        c = held + t
+        lo = max(first, c - window + 1 if window else 0, 0)
+        if c < first:
+            continue
+        for h in range(H):
+            g = h // (H // G)
+            s = (k[lo:c + 1, g] @ q[t, h]) * scale
+            out[t, h] = torch.softmax(s, dim=0) @ v[lo:c + 1, g]
+    return out
+
+
+def greedy(cfg, w, prompt, n_new):
+    tokens = list(prompt)
+    for _ in range(n_new):
+        tokens.append(int(forward(cfg, w, tokens)[-1].argmax()))
+    return tokens
+
+
+# ------------------------------------------------------------------ random models for the tests
+def random_config(width=48, vocab=61, heads=3, dim=8, vdim=12, q_rank=20, kv_rank=24, scale=0.3, ff=40, kinds=("dense", "moe", None),
+                  experts=6, identity=3, groups=(3, 2), top=3, expert_ff=16, shared_ff=20, side_dim=5, bigram=(53, 31, 17), emb_scale=0.7,
+                  eps=1e-5):
+    """config.json of a small model; ``kinds``: per layer the feed-forward ("dense", "moe" or None)"""
+    layers = []
+    for kind in kinds:
+        mlp = None
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": ff}
+        elif kind == "moe":
+            router = {"experts": experts, "identity": identity, "top": top}
+            if groups is not None:
+                router["groups"] = {"count": groups[0], "keep": groups[1]}
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": router}
+            if shared_ff:
+                mlp["shared"] = {"ff": shared_ff}
+        layers.append({"type": "latent_attention", "mlp": mlp,
+                       "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": scale}})
+    cfg = {"architecture": "Serotar", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": emb_scale}, "layers": layers}
+    if bigram:
+        cfg["embedding"]["bigram"] = {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}
+    if side_dim:
+        cfg["token_side"] = {"dim": side_dim}
+    return cfg
+
+
+def random_weights(cfg, seed, layer_scale=True, depth_average=True):
+    """checkpoint tensors (bfloat16, so that every dtype of the model starts from the same numbers)"""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def lin(o, i, gain=1.0):
+        return torch.randn(o, i, generator=g) * gain / math.sqrt(i)
+
+    def near(n, centre, spread):
+        return centre + spread * torch.randn(n, generator=g)
+
+    w = {"embed": torch.randn(V, W, generator=g), "head": lin(V, W), "final.norm": near((), 1.0, 0.1)}
+    bg = cfg["embedding"].get("bigram")
+    if bg:
+        w["bigram"] = torch.randn(bg["buckets"] + 1, W, generator=g) * 0.7
+    side = cfg.get("token_side")
+    if side:
+        w["side.embed"] = torch.randn(V, side["dim"] * len(cfg["layers"]), generator=g)
+    for i, lc in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lc["mixer"]
+        H, D, Dv = m["heads"], m["dim"], m["vdim"]
+        w[p + "mix.dq"], w[p + "mix.dq.norm"] = lin(m["q_rank"], W), near(m["q_rank"], 1.0, 0.2)
+        w[p + "mix.uq"] = lin(H * D, m["q_rank"], 2.0)
+        w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = lin(m["kv_rank"], W), near(m["kv_rank"], 1.0, 0.2)
+        w[p + "mix.uk"], w[p + "mix.uv"] = lin(H * D, m["kv_rank"], 2.0), lin(H * Dv, m["kv_rank"])
+        w[p + "mix.o"] = lin(W, H * Dv)
+        w[p + "norm1"] = near((), 1.0, 0.1)
+        if layer_scale:
+            w[p + "ls1"] = near(W, 0.6, 0.15)
+        mlp = lc["mlp"]
+        if mlp is not None:
+            w[p + "norm2"] = near((), 1.0, 0.1)
+            if layer_scale:
+                w[p + "ls2"] = near(W, 0.6, 0.15)
+            if mlp["kind"] == "dense":
+                w[p + "mlp.up"], w[p + "mlp.down"], w[p + "mlp.act"] = lin(mlp["ff"], W), lin(W, mlp["ff"]), torch.randn(2, generator=g)
+            else:
+                r = mlp["router"]
+                n_out = r["experts"] + r.get("identity", 0)
+                w[p + "mlp.router"], w[p + "mlp.correction"] = lin(n_out, W, 1.5), 0.05 * torch.randn(n_out, generator=g)
+                names = [f"e{e}." for e in range(r["experts"])] + (["shared."] if mlp.get("shared") else [])
+                for n in names:
+                    f = mlp["shared"]["ff"] if n == "shared." else mlp["expert"]["ff"]
+                    w[p + "mlp." + n + "gate"], w[p + "mlp." + n + "up"], w[p + "mlp." + n + "down"] = lin(f, W), lin(f, W), lin(W, f)
+        if side:
+            w[p + "side.gate"], w[p + "side.proj"], w[p + "side.norm"] = lin(side["dim"], W), lin(W, side["dim"]), near(W, 0.5, 0.1)
+        if depth_average:
+            c = torch.rand(i + 2, generator=g) + 0.2
+            c[-1] += 1.0
+            w[p + "dwa"] = c / c.sum() * near((), 1.0, 0.05)
+    return {k: v.to(torch.bfloat16) for k, v in w.items()}
