@@ -79,7 +79,8 @@ int mixers_soft_cap(int dtype, const void* x, long n, float cap, float* out, mix
 /* x[n, :] = table[ids[n], :] * scale + pair[row(n), :] as floats (x_copy, if given, gets the same; h, if given, the same in
  * dtype).  row(n) = (previous id * mul_prev + ids[n] * mul_cur) mod buckets; `buckets` itself for a sequence's first token
  * (position 0); the token before a call's first token is prev[b].  pair may be null (no second table).  ids: [B, S]; padding
- * slots (position < 0) give zeros. */
+ * slots (position < 0) give zeros.  pad may be null when slot0 > 0 (no new token is padding or a first token then): a step that
+ * is replayed from a CUDA graph has no current slot0 to give. */
 int mixers_embed_pair(int dtype, const void* table, float scale, const void* pair, long buckets, long mul_prev, long mul_cur,
                       const int64_t* ids, const int64_t* prev, int B, int S, int width, int slot0, const int32_t* pad, float* x,
                       float* x_copy, void* h, mixers_stream_t stream);

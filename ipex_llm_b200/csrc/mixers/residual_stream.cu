@@ -28,7 +28,7 @@ __global__ void embed_pair_kernel(const T* __restrict__ table, float scale, cons
                                   const int32_t* __restrict__ pad, float* __restrict__ x, float* __restrict__ x_copy, T* __restrict__ h) {
     const long n = blockIdx.x;
     const int b = (int)(n / S), t = (int)(n - (long)b * S);
-    const int pos = slot0 + t - pad[b];
+    const int pos = slot0 + t - (pad ? pad[b] : 0);           // pad may be null: no new token is padding
     const long id = ids[n];
     long row = -1;
     if (pair && pos >= 0) {

@@ -287,9 +287,11 @@ class SerotarForCausalLM(PreTrainedModel, GenerationMixin):
         stack = torch.empty(n_layers + 1, B * S, cfg.width, dtype=torch.float32, device=dev) if cfg.depth_average else None
         bg = cfg.bigram
         prev = cache.previous_tokens(B, dev)
+        # padding and first tokens only occur in a batch's first call; later calls (a replayed step among them, whose slot
+        # number is the one at recording time) say so by passing no padding
         x, h = ops.embed_pair(core.embed_tokens.weight, cfg.embedding.get("scale", 1.0), core.pair_embed.weight if bg else None,
                               bg["buckets"] if bg else 0, bg["mul_prev"] if bg else 0, bg["mul_cur"] if bg else 0, input_ids, prev,
-                              cache.seen, cache.pad, dtype, x_copy=stack[0] if stack is not None else None)
+                              cache.seen, cache.pad if cache.seen == 0 else None, dtype, x_copy=stack[0] if stack is not None else None)
         prev.copy_(input_ids[:, -1])                                         # the pair of the next call's first token
         for i, layer in enumerate(core.layers):
             def add(y, gain, vec, last):
