@@ -115,11 +115,15 @@ int mixers_latent_prepare(int dtype, const void* proj, int B, int S, int ld, int
  * index j, row b, kv head g at k + b * k_bs + j * k_ps + g * k_hs (strides in elements).  The query at storage index c = held
  * + t sees the keys j <= c of its row that are not padding (j + shift >= pad[b]) and, if window > 0, c - j < window.  Scores
  * (q . k) * scale and the softmax weights are 32-bit.  out[n, out_col + h * vdim + :] in dtype (zeros for padding queries).
- * allow_tensor_cores: 16-bit models may take the tensor-core kernel for S >= 16 (head sizes multiples of 16, <= 256). */
+ * allow_tensor_cores: 16-bit models may take the tensor-core kernels: for S >= 16 one block per 64 tokens of a head (head sizes
+ * multiples of 16, <= 256); for S <= 16 and at least 4 query heads per kv head one pass over the keys for all heads of a
+ * group, the keys split over blocks (dim a multiple of 16, <= 512; vdim 128, 256 or 512), which needs `ws`:
+ * mixers_softmax_attention_workspace(...) floats (0: these sizes never take that kernel).  dyn as above. */
 int mixers_softmax_attention(int dtype, const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                              long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
                              int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
-                             const int32_t* dyn, int allow_tensor_cores, mixers_stream_t stream);
+                             const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream);
+long mixers_softmax_attention_workspace(int dtype, int B, int S, int heads, int kv_heads, int dim, int vdim);
 
 /* Router of a mixture of experts.  z = router h (32-bit; router [n_out, width], h [n_rows, width] in dtype), s = softmax(z) over
  * all n_out outputs, choice = s + correction.  Outputs [g * n_out / groups, (g + 1) * n_out / groups) are group g; groups are

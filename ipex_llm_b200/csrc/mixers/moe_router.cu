@@ -9,7 +9,7 @@
 #include "mixers_common.cuh"
 #include <math.h>
 
-constexpr int ROUTER_WARPS = 4;
+constexpr int ROUTER_WARPS = 8;
 
 // lowest index among the largest values of vals[0..n) that are still allowed (taken[i] == 0); one warp
 __device__ __forceinline__ int warp_argmax(const float* vals, const unsigned char* blocked, int n, int lane) {
@@ -29,32 +29,48 @@ __device__ __forceinline__ int warp_argmax(const float* vals, const unsigned cha
     return at;
 }
 
-// one warp per token
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __restrict__ b, int n, int lane) {
+    float s = 0.0f;
+    if constexpr (sizeof(T) == 2) {
+        if ((n & 7) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+            for (int c = lane * 8; c < n; c += 256) {
+                uint4 va = *reinterpret_cast<const uint4*>(a + c), vb = *reinterpret_cast<const uint4*>(b + c);
+                const T* ea = reinterpret_cast<const T*>(&va);
+                const T* eb = reinterpret_cast<const T*>(&vb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s += to_f(ea[i]) * to_f(eb[i]);
+            }
+            return warp_sum(s);
+        }
+    }
+    for (int c = lane; c < n; c += 32) s += to_f(a[c]) * to_f(b[c]);
+    return warp_sum(s);
+}
+
+// one block of ROUTER_WARPS warps per token: the warps share the router's rows (16-byte loads), warp 0 then chooses
 template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32) grouped_router_kernel(
         const T* __restrict__ h, long n_rows, int width, const T* __restrict__ router, const T* __restrict__ correction, int n_out, int groups,
         int keep, int top, int32_t* __restrict__ idx_out, float* __restrict__ w_out) {
     extern __shared__ float router_sh[];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per_warp = 2 * n_out + groups + ((n_out + groups + 3) / 4);
-    float* score = router_sh + (long)wid * per_warp;        // softmax scores
+    float* score = router_sh;                               // logits, then softmax scores
     float* choice = score + n_out;                          // scores + correction
     float* gbest = choice + n_out;
     unsigned char* blocked = reinterpret_cast<unsigned char*>(gbest + groups);      // [n_out] experts, then [groups]
     unsigned char* gblocked = blocked + n_out;
-    const long n = blockIdx.x * (long)ROUTER_WARPS + wid;
-    if (n >= n_rows) return;
+    const long n = blockIdx.x;
     const T* hr = h + n * width;
-    float big = -INFINITY;
-    for (int e = 0; e < n_out; ++e) {
-        const T* r = router + (long)e * width;
-        float s = 0.0f;
-        for (int c = lane; c < width; c += 32) s += to_f(hr[c]) * to_f(r[c]);
-        s = warp_sum(s);
+    for (int e = wid; e < n_out; e += ROUTER_WARPS) {
+        const float s = warp_dot(router + (long)e * width, hr, width, lane);
         if (lane == 0) score[e] = s;
-        big = fmaxf(big, s);
     }
-    __syncwarp();
+    __syncthreads();
+    if (wid != 0) return;
+    float big = -INFINITY;
+    for (int e = lane; e < n_out; e += 32) big = fmaxf(big, score[e]);
+    big = warp_max(big);
     float sum = 0.0f;
     for (int e = lane; e < n_out; e += 32) sum += expf(score[e] - big);
     sum = warp_sum(sum);
@@ -89,25 +105,6 @@ __global__ void __launch_bounds__(ROUTER_WARPS * 32) grouped_router_kernel(
         }
         __syncwarp();
     }
-}
-
-template <typename T>
-__device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __restrict__ b, int n, int lane) {
-    float s = 0.0f;
-    if constexpr (sizeof(T) == 2) {
-        if ((n & 7) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0) {
-            for (int c = lane * 8; c < n; c += 256) {
-                uint4 va = *reinterpret_cast<const uint4*>(a + c), vb = *reinterpret_cast<const uint4*>(b + c);
-                const T* ea = reinterpret_cast<const T*>(&va);
-                const T* eb = reinterpret_cast<const T*>(&vb);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s += to_f(ea[i]) * to_f(eb[i]);
-            }
-            return warp_sum(s);
-        }
-    }
-    for (int c = lane; c < n; c += 32) s += to_f(a[c]) * to_f(b[c]);
-    return warp_sum(s);
 }
 
 // grid (ceil(ff / 8), n_rows * top), 8 warps a block, one warp per row of the chosen expert's gate and up matrices.
@@ -179,11 +176,9 @@ extern "C" int mixers_grouped_router(int dtype, const void* h, long n_rows, int 
                                      int groups, int keep, int top, int32_t* idx_out, float* w_out, mixers_stream_t stream) {
     if (n_rows <= 0) return 0;
     if (groups < 1 || n_out % groups != 0 || keep < 1 || keep > groups || top < 1) return (int)cudaErrorInvalidValue;
-    const int per_warp = 2 * n_out + groups + ((n_out + groups + 3) / 4);
-    size_t smem = (size_t)ROUTER_WARPS * per_warp * sizeof(float);
+    size_t smem = (size_t)(2 * n_out + groups + ((n_out + groups + 3) / 4)) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    unsigned blocks = (unsigned)((n_rows + ROUTER_WARPS - 1) / ROUTER_WARPS);
-    MIXERS_DISPATCH(dtype, grouped_router_kernel<T><<<blocks, ROUTER_WARPS * 32, smem, (cudaStream_t)stream>>>(
+    MIXERS_DISPATCH(dtype, grouped_router_kernel<T><<<(unsigned)n_rows, ROUTER_WARPS * 32, smem, (cudaStream_t)stream>>>(
         (const T*)h, n_rows, width, (const T*)router, (const T*)correction, n_out, groups, keep, top, idx_out, w_out));
     return mixers_status();
 }

@@ -170,8 +170,7 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
         float scale, T* __restrict__ out, long ld_out, int out_col) {
     extern __shared__ __align__(16) unsigned char sa_tc_sh[];
     const int kstride = dim + 8, vstride = vdim + 8;        // elements
-    T* Ks = reinterpret_cast<T*>(sa_tc_sh);                 // [SA_KEYS][kstride]
-    T* Vs = Ks + SA_KEYS * kstride;                         // [SA_KEYS][vstride]
+    T* Ks = reinterpret_cast<T*>(sa_tc_sh);                 // two stages of [SA_KEYS][kstride] keys + [SA_KEYS][vstride] values
     // the last query tiles first: they see the most keys
     const int b = blockIdx.z, h = blockIdx.y, t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * SA_ROWS;
     const int g = h / (heads / kv_heads);
@@ -223,99 +222,118 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
     const T* vbase = v + b * v_bs + g * v_hs;
     const int kchunks = dim >> 3, vchunks = vdim >> 3;      // 16-byte pieces per row
 
-    for (int jt = j_start; jt <= c_hi; jt += SA_KEYS) {
-        __syncthreads();                                    // the previous tile has been consumed
+    // two stages of K / V tiles: the next tile's copies (cp.async, 16 bytes each) are in flight while this one is multiplied
+    auto load_tile = [&](int stage, int jt) {
+        T* kd_ = Ks + stage * SA_KEYS * (kstride + vstride);
+        T* vd_ = kd_ + SA_KEYS * kstride;
         for (int id = tid; id < SA_KEYS * kchunks; id += 128) {
             int r = id / kchunks, cch = id - r * kchunks;
             int j = jt + r <= c_hi ? jt + r : c_hi;         // rows past the end repeat the last one (their weights are zero)
-            *reinterpret_cast<uint4*>(Ks + r * kstride + cch * 8) = *reinterpret_cast<const uint4*>(kbase + j * k_ps + cch * 8);
+            uint32_t dst = (uint32_t)__cvta_generic_to_shared(kd_ + r * kstride + cch * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(kbase + j * k_ps + cch * 8));
         }
         for (int id = tid; id < SA_KEYS * vchunks; id += 128) {
             int r = id / vchunks, cch = id - r * vchunks;
             int j = jt + r <= c_hi ? jt + r : c_hi;
-            *reinterpret_cast<uint4*>(Vs + r * vstride + cch * 8) = *reinterpret_cast<const uint4*>(vbase + j * v_ps + cch * 8);
+            uint32_t dst = (uint32_t)__cvta_generic_to_shared(vd_ + r * vstride + cch * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(vbase + j * v_ps + cch * 8));
         }
-        __syncthreads();
-        if (jt > warp_hi || jt + SA_KEYS - 1 < warp_lo) continue;        // no row of this warp sees the tile
-        float sc[4][4];
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    if (j_start <= c_hi) load_tile(0, j_start);
+    int stage = 0;
+    for (int jt = j_start; jt <= c_hi; jt += SA_KEYS, stage ^= 1) {
+        if (jt + SA_KEYS <= c_hi) {
+            load_tile(stage ^ 1, jt + SA_KEYS);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();                                    // this tile has arrived for every thread
+        const T* Kt = Ks + stage * SA_KEYS * (kstride + vstride);
+        const T* Vt = Kt + SA_KEYS * kstride;
+        if (!(jt > warp_hi || jt + SA_KEYS - 1 < warp_lo)) {               // some row of this warp sees the tile
+            float sc[4][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
+            for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) sc[nt][i] = 0.0f;
-            const T* krow = Ks + (nt * 8 + gr) * kstride + 2 * tq;
+                for (int i = 0; i < 4; ++i) sc[nt][i] = 0.0f;
+                const T* krow = Kt + (nt * 8 + gr) * kstride + 2 * tq;
 #pragma unroll
-            for (int kd = 0; kd < KDMAX; ++kd) {
-                if (kd < kdn) {
-                    uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + kd * 16);
-                    uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + kd * 16 + 8);
-                    SaMma<T>::mma(sc[nt], qa[kd], b0, b1);
+                for (int kd = 0; kd < KDMAX; ++kd) {
+                    if (kd < kdn) {
+                        uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + kd * 16);
+                        uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + kd * 16 + 8);
+                        SaMma<T>::mma(sc[nt], qa[kd], b0, b1);
+                    }
                 }
             }
-        }
-        // scores -> masked, scaled; the rows' new maxima
-        float tmax[2] = {-INFINITY, -INFINITY};
+            // scores -> masked, scaled; the rows' new maxima
+            float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
+            for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int j = jt + nt * 8 + 2 * tq + (i & 1);
-                const int r = i >> 1;
-                const float s = (j >= row_lo[r] && j <= row_c[r]) ? sc[nt][i] * scale : -INFINITY;
-                sc[nt][i] = s;
-                tmax[r] = fmaxf(tmax[r], s);
+                for (int i = 0; i < 4; ++i) {
+                    const int j = jt + nt * 8 + 2 * tq + (i & 1);
+                    const int r = i >> 1;
+                    const float s = (j >= row_lo[r] && j <= row_c[r]) ? sc[nt][i] * scale : -INFINITY;
+                    sc[nt][i] = s;
+                    tmax[r] = fmaxf(tmax[r], s);
+                }
             }
-        }
-        float corr[2], m_new[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-            m_new[r] = fmaxf(m_run[r], tmax[r]);
-            corr[r] = m_new[r] == -INFINITY ? 1.0f : __expf(m_run[r] - m_new[r]);
-            m_run[r] = m_new[r];
-            l_run[r] *= corr[r];
-        }
-#pragma unroll
-        for (int nd = 0; nd < NDMAX; ++nd) {
-            oacc[nd][0] *= corr[0]; oacc[nd][1] *= corr[0];
-            oacc[nd][2] *= corr[1]; oacc[nd][3] *= corr[1];
-        }
-        uint32_t ph[2][4], pl[2][4];
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            float p[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = i >> 1;
-                p[i] = sc[nt][i] == -INFINITY ? 0.0f : __expf(sc[nt][i] - m_new[r]);
-                l_run[r] += p[i];
-            }
-            const int ks = nt >> 1, half = nt & 1;
+            float corr[2], m_new[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                uint32_t hi = SaMma<T>::pack(p[2 * r], p[2 * r + 1]);
-                float2 back = SaMma<T>::unpack(hi);
-                ph[ks][2 * half + r] = hi;
-                pl[ks][2 * half + r] = SaMma<T>::pack(p[2 * r] - back.x, p[2 * r + 1] - back.y);
+                tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+                tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+                m_new[r] = fmaxf(m_run[r], tmax[r]);
+                corr[r] = m_new[r] == -INFINITY ? 1.0f : __expf(m_run[r] - m_new[r]);
+                m_run[r] = m_new[r];
+                l_run[r] *= corr[r];
             }
-        }
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
+            for (int nd = 0; nd < NDMAX; ++nd) {
+                oacc[nd][0] *= corr[0]; oacc[nd][1] *= corr[0];
+                oacc[nd][2] *= corr[1]; oacc[nd][3] *= corr[1];
+            }
+            uint32_t ph[2][4], pl[2][4];
 #pragma unroll
-            for (int np = 0; np < NDMAX / 2; ++np) {
-                if (2 * np < ndn) {
-                    uint32_t v0, v1, v2, v3;
-                    const T* vaddr = Vs + (ks * 16 + (lane & 15)) * vstride + np * 16 + ((lane >> 4) << 3);
-                    uint32_t sa = (uint32_t)__cvta_generic_to_shared(vaddr);
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                                 : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(sa));
-                    SaMma<T>::mma(oacc[2 * np], ph[ks], v0, v1);
-                    SaMma<T>::mma(oacc[2 * np], pl[ks], v0, v1);
-                    SaMma<T>::mma(oacc[2 * np + 1], ph[ks], v2, v3);
-                    SaMma<T>::mma(oacc[2 * np + 1], pl[ks], v2, v3);
+            for (int nt = 0; nt < 4; ++nt) {
+                float p[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = i >> 1;
+                    p[i] = sc[nt][i] == -INFINITY ? 0.0f : __expf(sc[nt][i] - m_new[r]);
+                    l_run[r] += p[i];
+                }
+                const int ks = nt >> 1, half = nt & 1;
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    uint32_t hi = SaMma<T>::pack(p[2 * r], p[2 * r + 1]);
+                    float2 back = SaMma<T>::unpack(hi);
+                    ph[ks][2 * half + r] = hi;
+                    pl[ks][2 * half + r] = SaMma<T>::pack(p[2 * r] - back.x, p[2 * r + 1] - back.y);
+                }
+            }
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+                for (int np = 0; np < NDMAX / 2; ++np) {
+                    if (2 * np < ndn) {
+                        uint32_t v0, v1, v2, v3;
+                        const T* vaddr = Vt + (ks * 16 + (lane & 15)) * vstride + np * 16 + ((lane >> 4) << 3);
+                        uint32_t sa = (uint32_t)__cvta_generic_to_shared(vaddr);
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                                     : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(sa));
+                        SaMma<T>::mma(oacc[2 * np], ph[ks], v0, v1);
+                        SaMma<T>::mma(oacc[2 * np], pl[ks], v0, v1);
+                        SaMma<T>::mma(oacc[2 * np + 1], ph[ks], v2, v3);
+                        SaMma<T>::mma(oacc[2 * np + 1], pl[ks], v2, v3);
+                    }
                 }
             }
         }
+        __syncthreads();                                    // the tile has been consumed: its stage may be overwritten
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -336,6 +354,272 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
     }
 }
 
+// ---- few new tokens of a 16-bit model whose query heads share key / value heads (one shared head in the extreme: a latent
+// cache read as key AND value): the 16 rows of an MMA tile are (token, head) pairs of one group, so ONE pass over the keys
+// serves them all.  grid (key splits, 16-row tiles x kv heads, batch); a block of 8 warps walks its range of keys 64 at a
+// time: the tile of keys in shared memory (once, when keys and values are the same tensor), S = Q K^T with each warp taking 8
+// keys, the scaled and masked scores through shared memory, then every warp forms the rows' running maxima and the weights
+// (as the sum of two 16-bit numbers, like the prompt kernel) and multiplies them into ITS 1/8 of the value columns.  Each
+// block leaves (max, sum, weighted values) of its key range in the workspace; shared_head_merge_kernel adds the ranges up.
+constexpr int SH_KEYS = 64, SH_SSTRIDE = 72, SH_MIN_CHUNK = 128, SH_MAX_SPLITS = 32;
+
+template <typename T, int NT, bool SAME>                   // vdim = 64 NT (each warp owns 8 NT value columns)
+__global__ void __launch_bounds__(256) shared_head_attention_kernel(
+        const T* __restrict__ q, long q_ld, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
+        long v_hs, int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* __restrict__ pad, int window, float scale,
+        float* __restrict__ ws, int splits, int tiles, const int32_t* __restrict__ dyn) {
+    constexpr int vdim = 64 * NT;
+    extern __shared__ __align__(16) unsigned char sh_raw[];
+    const int kstride = dim + 8, vstride = vdim + 8;
+    T* Qs = reinterpret_cast<T*>(sh_raw);                   // [16][kstride]
+    T* Ks = Qs + 16 * kstride;                              // [SH_KEYS][kstride]
+    T* Vs = SAME ? Ks : Ks + SH_KEYS * kstride;             // [SH_KEYS][vstride]
+    float* Ss = reinterpret_cast<float*>(Ks + SH_KEYS * kstride + (SAME ? 0 : SH_KEYS * vstride));      // [16][SH_SSTRIDE]
+    int* row_c = reinterpret_cast<int*>(Ss + 16 * SH_SSTRIDE);                                           // [16] newest visible key, -1: none
+    int* row_lo = row_c + 16;                                                                            // [16] oldest visible key
+    if (dyn) held = dyn[0];
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31, gr = lane >> 2, tq = lane & 3;
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int g = blockIdx.y / tiles, tile = blockIdx.y - g * tiles;
+    const int gs = heads / kv_heads, n_rows = S * gs;
+    const int first_real = pad[b] - shift;
+    if (tid < 16) {
+        const int r = tile * 16 + tid;
+        int c = -1, lo = 0;
+        if (r < n_rows) {
+            c = held + r / gs;
+            lo = window > 0 ? c - window + 1 : 0;
+            if (lo < first_real) lo = first_real;
+            if (lo < 0) lo = 0;
+            if (c < first_real) c = -1;
+        }
+        row_c[tid] = c;
+        row_lo[tid] = lo;
+    }
+    // the queries of this tile's rows, zeros for rows that do not exist
+    const int qchunks = dim >> 3;
+    for (int id = tid; id < 16 * qchunks; id += 256) {
+        const int i = id / qchunks, cch = id - i * qchunks;
+        const int r = tile * 16 + i;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((long)b * S + r / gs) * q_ld + (long)(g * gs + r % gs) * dim + cch * 8);
+        *reinterpret_cast<uint4*>(Qs + i * kstride + cch * 8) = val;
+    }
+    __syncthreads();
+    int lo_all = 0x7fffffff, hi_all = -1;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        if (row_c[i] >= 0) { lo_all = min(lo_all, row_lo[i]); hi_all = max(hi_all, row_c[i]); }
+    }
+    const int my_c[2] = {row_c[gr], row_c[gr + 8]}, my_lo[2] = {row_lo[gr], row_lo[gr + 8]};
+    // this block's range of keys
+    int j_lo = 0, j_hi = -1;
+    if (hi_all >= 0) {
+        const int nkeys = hi_all - lo_all + 1;
+        int chunk = ((nkeys + splits - 1) / splits + SH_KEYS - 1) / SH_KEYS * SH_KEYS;
+        if (chunk < SH_MIN_CHUNK) chunk = SH_MIN_CHUNK;
+        j_lo = lo_all + split * chunk;
+        j_hi = min(hi_all, j_lo + chunk - 1);
+    }
+    float oacc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) oacc[nt][i] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const T* kbase = k + b * k_bs + g * k_hs;
+    const T* vbase = v + b * v_bs + g * v_hs;
+    const int kchunks = dim >> 3, vchunks = vdim >> 3, kdn = dim >> 4;
+
+    for (int jt = j_lo; jt <= j_hi; jt += SH_KEYS) {
+        __syncthreads();                                    // the previous tile (and its scores) has been consumed
+        for (int id = tid; id < SH_KEYS * kchunks; id += 256) {
+            const int r = id / kchunks, cch = id - r * kchunks;
+            const int j = jt + r <= j_hi ? jt + r : j_hi;   // rows past the end repeat the last one (their weights are zero)
+            *reinterpret_cast<uint4*>(Ks + r * kstride + cch * 8) = *reinterpret_cast<const uint4*>(kbase + j * k_ps + cch * 8);
+        }
+        if (!SAME) {
+            for (int id = tid; id < SH_KEYS * vchunks; id += 256) {
+                const int r = id / vchunks, cch = id - r * vchunks;
+                const int j = jt + r <= j_hi ? jt + r : j_hi;
+                *reinterpret_cast<uint4*>(Vs + r * vstride + cch * 8) = *reinterpret_cast<const uint4*>(vbase + j * v_ps + cch * 8);
+            }
+        }
+        __syncthreads();
+        {   // scores of keys 8 wid .. 8 wid + 7 for the 16 rows
+            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const T* qrow = Qs + gr * kstride + 2 * tq;
+            const T* krow = Ks + (wid * 8 + gr) * kstride + 2 * tq;
+            for (int kd = 0; kd < kdn; ++kd) {
+                uint32_t a[4];
+                a[0] = *reinterpret_cast<const uint32_t*>(qrow + kd * 16);
+                a[1] = *reinterpret_cast<const uint32_t*>(qrow + 8 * kstride + kd * 16);
+                a[2] = *reinterpret_cast<const uint32_t*>(qrow + kd * 16 + 8);
+                a[3] = *reinterpret_cast<const uint32_t*>(qrow + 8 * kstride + kd * 16 + 8);
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + kd * 16);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + kd * 16 + 8);
+                SaMma<T>::mma(sc, a, b0, b1);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float2 out;
+                const int j = jt + wid * 8 + 2 * tq;
+                out.x = (j >= my_lo[r] && j <= my_c[r] && j <= j_hi) ? sc[2 * r] * scale : -INFINITY;
+                out.y = (j + 1 >= my_lo[r] && j + 1 <= my_c[r] && j + 1 <= j_hi) ? sc[2 * r + 1] * scale : -INFINITY;
+                *reinterpret_cast<float2*>(Ss + (gr + 8 * r) * SH_SSTRIDE + wid * 8 + 2 * tq) = out;
+            }
+        }
+        __syncthreads();
+        // every warp: the rows' maxima and weights over the 64 keys (a lane holds the 16 keys of its A fragments per row)
+        float2 sv[2][4][2];
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const float2 x = *reinterpret_cast<const float2*>(Ss + (gr + 8 * r) * SH_SSTRIDE + ks * 16 + half * 8 + 2 * tq);
+                    sv[r][ks][half] = x;
+                    tmax[r] = fmaxf(tmax[r], fmaxf(x.x, x.y));
+                }
+        float corr[2], m_new[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+            m_new[r] = fmaxf(m_run[r], tmax[r]);
+            corr[r] = m_new[r] == -INFINITY ? 1.0f : __expf(m_run[r] - m_new[r]);
+            m_run[r] = m_new[r];
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            oacc[nt][0] *= corr[0]; oacc[nt][1] *= corr[0];
+            oacc[nt][2] *= corr[1]; oacc[nt][3] *= corr[1];
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const float2 x = sv[r][ks][half];
+                    const float p0 = x.x == -INFINITY ? 0.0f : __expf(x.x - m_new[r]);
+                    const float p1 = x.y == -INFINITY ? 0.0f : __expf(x.y - m_new[r]);
+                    l_run[r] += p0 + p1;
+                    const uint32_t hi = SaMma<T>::pack(p0, p1);
+                    const float2 back = SaMma<T>::unpack(hi);
+                    ph[2 * half + r] = hi;
+                    pl[2 * half + r] = SaMma<T>::pack(p0 - back.x, p1 - back.y);
+                }
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t v0, v1, v2, v3;
+                const T* vaddr = Vs + (ks * 16 + (lane & 15)) * (SAME ? kstride : vstride) + wid * (8 * NT) + np * 16 + ((lane >> 4) << 3);
+                const uint32_t sa = (uint32_t)__cvta_generic_to_shared(vaddr);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(sa));
+                SaMma<T>::mma(oacc[2 * np], ph, v0, v1);
+                SaMma<T>::mma(oacc[2 * np], pl, v0, v1);
+                SaMma<T>::mma(oacc[2 * np + 1], ph, v2, v3);
+                SaMma<T>::mma(oacc[2 * np + 1], pl, v2, v3);
+            }
+        }
+    }
+    // this range's share: per row the maximum, the sum, and the weighted values
+    float* base = ws + (((long)b * gridDim.y + blockIdx.y) * splits + split) * (16L * (vdim + 2));
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float l = l_run[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        float* rowp = base + (gr + 8 * r) * (long)(vdim + 2);
+        if (wid == 0 && tq == 0) { rowp[0] = m_run[r]; rowp[1] = l; }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            *reinterpret_cast<float2*>(rowp + 2 + wid * (8 * NT) + nt * 8 + 2 * tq) = make_float2(oacc[nt][2 * r], oacc[nt][2 * r + 1]);
+    }
+}
+
+// grid (16 x 16-row tiles x kv heads, batch): one block per row adds up the key ranges' shares.  Warp 0 turns the ranges'
+// maxima into factors; then every thread owns two neighbouring columns and reads them from all ranges (independent loads).
+template <typename T>
+__global__ void __launch_bounds__(128) shared_head_merge_kernel(const float* __restrict__ ws, int S, int heads, int kv_heads, int vdim, int splits,
+                                                                int tiles, T* __restrict__ out, long ld_out, int out_col) {
+    __shared__ float factor[SH_MAX_SPLITS];
+    __shared__ float inv_total;
+    const int y = blockIdx.x >> 4, i = blockIdx.x & 15, lane = threadIdx.x & 31;
+    const int b = blockIdx.y, g = y / tiles, tile = y - g * tiles;
+    const int gs = heads / kv_heads;
+    const int r = tile * 16 + i;
+    if (r >= S * gs) return;
+    const long sstride = 16L * (vdim + 2);
+    const float* base = ws + ((long)b * (gridDim.x >> 4) + y) * splits * sstride + i * (long)(vdim + 2);
+    if (threadIdx.x < 32) {
+        const float m = lane < splits ? base[lane * sstride] : -INFINITY;
+        const float l = lane < splits ? base[lane * sstride + 1] : 0.0f;
+        const float big = warp_max(m);
+        const float f = m == -INFINITY ? 0.0f : __expf(m - big);
+        const float total = warp_sum(l * f);
+        factor[lane] = f;
+        if (lane == 0) inv_total = total > 0.0f ? 1.0f / total : 0.0f;
+    }
+    __syncthreads();
+    T* dst = out + ((long)b * S + r / gs) * ld_out + out_col + (long)(g * gs + r % gs) * vdim;
+    for (int col = 2 * threadIdx.x; col < vdim; col += 256) {
+        float sx = 0.0f, sy = 0.0f;
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) {
+            const float2 o = *reinterpret_cast<const float2*>(base + s * sstride + 2 + col);
+            sx += o.x * factor[s];
+            sy += o.y * factor[s];
+        }
+        dst[col] = from_f<T>(sx * inv_total);
+        dst[col + 1] = from_f<T>(sy * inv_total);
+    }
+}
+
+static int shared_head_splits(int B, int S, int heads, int kv_heads) {
+    const int tiles = (S * (heads / kv_heads) + 15) / 16;
+    long blocks = (long)B * kv_heads * tiles;
+    long s = (2L * 148 + blocks - 1) / blocks;
+    return (int)(s < 1 ? 1 : (s > SH_MAX_SPLITS ? SH_MAX_SPLITS : s));
+}
+
+static bool shared_head_ok(int dtype, int S, int heads, int kv_heads, int dim, int vdim) {
+    return dtype != 0 && kv_heads >= 1 && heads % kv_heads == 0 && heads / kv_heads >= 4 && S <= 16 && dim % 16 == 0 && dim <= 512 &&
+           (vdim == 128 || vdim == 256 || vdim == 512);
+}
+
+template <typename T, int NT>
+static int launch_shared_head(const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs,
+                              int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* pad, int window, float scale,
+                              void* out, long ld_out, int out_col, const int32_t* dyn, float* ws, cudaStream_t stream) {
+    const int vdim = 64 * NT;
+    const int tiles = (S * (heads / kv_heads) + 15) / 16, splits = shared_head_splits(B, S, heads, kv_heads);
+    const bool same = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
+    size_t smem = (size_t)(16 + SH_KEYS) * (dim + 8) * sizeof(T) + (same ? 0 : (size_t)SH_KEYS * (vdim + 8) * sizeof(T)) +
+                  16 * SH_SSTRIDE * sizeof(float) + 32 * sizeof(int);
+    dim3 grid(splits, tiles * kv_heads, B);
+    cudaError_t err;
+    if (same) {
+        auto fn = shared_head_attention_kernel<T, NT, true>;
+        if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
+        fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
+                                        shift, pad, window, scale, ws, splits, tiles, dyn);
+    } else {
+        auto fn = shared_head_attention_kernel<T, NT, false>;
+        if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
+        fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
+                                        shift, pad, window, scale, ws, splits, tiles, dyn);
+    }
+    if ((err = cudaGetLastError()) != cudaSuccess) return (int)err;
+    shared_head_merge_kernel<T><<<dim3(16 * tiles * kv_heads, B), 128, 0, stream>>>(ws, S, heads, kv_heads, vdim, splits, tiles, (T*)out, ld_out, out_col);
+    return mixers_status();
+}
+
 #define SA_TC_PARAMS const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs, \
     int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* pad, int window, float scale, void* out,     \
     long ld_out, int out_col, cudaStream_t stream
@@ -344,8 +628,12 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
 
 template <typename T, int KDMAX, int NDMAX>
 static int launch_softmax_tc(SA_TC_PARAMS) {
-    size_t smem = (size_t)SA_KEYS * (dim + 8 + vdim + 8) * sizeof(T);
+    size_t smem = 2 * (size_t)SA_KEYS * (dim + 8 + vdim + 8) * sizeof(T);
     dim3 grid((S + SA_ROWS - 1) / SA_ROWS, heads, B);
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(softmax_attention_tc_kernel<T, KDMAX, NDMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+    }
     softmax_attention_tc_kernel<T, KDMAX, NDMAX><<<grid, 128, smem, stream>>>(
         (const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
         scale, (T*)out, ld_out, out_col);
@@ -374,7 +662,7 @@ extern "C" int mixers_latent_prepare(int dtype, const void* proj, int B, int S, 
 extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                                         long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
                                         int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
-                                        const int32_t* dyn, int allow_tensor_cores, mixers_stream_t stream_) {
+                                        const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream_) {
     if (B <= 0 || S <= 0) return 0;
     cudaStream_t stream = (cudaStream_t)stream_;
     const int dim4 = (dim + 3) & ~3;
@@ -384,6 +672,15 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, con
     auto mult8 = [](long s) { return (s & 7) == 0; };
     const bool rows16 = esz == 2 && mult8(k_bs) && mult8(k_ps) && mult8(k_hs) && mult8(v_bs) && mult8(v_ps) && mult8(v_hs) &&
                         ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && (dim & 7) == 0;
+    if (allow_tensor_cores && ws && rows16 && shared_head_ok(dtype, S, heads, kv_heads, dim, vdim) && (q_ld & 7) == 0 && ((uintptr_t)q & 15) == 0 &&
+        (ld_out & 1) == 0 && (out_col & 1) == 0) {
+#define SH_ARGS q, q_ld, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, scale, out, ld_out, out_col, dyn, ws, stream
+        if (dtype == 1) return vdim == 128 ? launch_shared_head<__nv_bfloat16, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__nv_bfloat16, 4>(SH_ARGS)
+                                                                                                       : launch_shared_head<__nv_bfloat16, 8>(SH_ARGS);
+        return vdim == 128 ? launch_shared_head<__half, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__half, 4>(SH_ARGS)
+                                                                                  : launch_shared_head<__half, 8>(SH_ARGS);
+#undef SH_ARGS
+    }
     if (allow_tensor_cores && dtype != 0 && !dyn && S >= 16 && rows16 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 256 && vdim <= 256 &&
         (q_ld & 1) == 0 && ((uintptr_t)q & 3) == 0 && (ld_out & 1) == 0 && (out_col & 1) == 0) {
         if (dtype == 1) return softmax_tc<__nv_bfloat16>(SA_TC_ARGS);
@@ -394,4 +691,11 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, con
         (const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
         scale, (T*)out, ld_out, out_col, dyn, rows16 ? 1 : 0));
     return mixers_status();
+}
+
+// floats of workspace that mixers_softmax_attention wants for these sizes (0: none; it then needs no workspace)
+extern "C" long mixers_softmax_attention_workspace(int dtype, int B, int S, int heads, int kv_heads, int dim, int vdim) {
+    if (B <= 0 || S <= 0 || !shared_head_ok(dtype, S, heads, kv_heads, dim, vdim)) return 0;
+    const long tiles = (S * (heads / kv_heads) + 15) / 16;
+    return (long)B * kv_heads * tiles * shared_head_splits(B, S, heads, kv_heads) * 16L * (vdim + 2);
 }

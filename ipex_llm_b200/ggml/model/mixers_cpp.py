@@ -46,7 +46,7 @@ _SIGNATURES = {
     "mixers_latent_prepare": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_softmax_attention": [_c_int, _c_ptr, _c_long, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long] + [_c_int] * 8
-                                + [_c_ptr, _c_int, _c_float, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr],
+                                + [_c_ptr, _c_int, _c_float, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "mixers_grouped_router": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_small": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                          _c_ptr],
@@ -66,6 +66,8 @@ def lib():
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(loaded, name)
             fn.argtypes, fn.restype = argtypes, _c_int
+        loaded.mixers_softmax_attention_workspace.argtypes = [_c_int] * 7
+        loaded.mixers_softmax_attention_workspace.restype = _c_long
         _lib, LIB_PATH = loaded, path
     return _lib
 

@@ -264,6 +264,9 @@ def _plan(model, inputs, generation_config, kwargs):
     mask = kwargs.get("attention_mask")
     if mask is not None and not bool(mask.to(torch.bool).all()):
         return None                                           # padded batches: positions differ per sequence
+    mlp0 = getattr(getattr(getattr(model, "model", None), "layers", [None])[0], "mlp", None)
+    if input_ids.shape[0] > 1 and hasattr(mlp0, "experts") and hasattr(mlp0, "gate"):
+        return None                                           # several tokens of a mixture of experts are sorted on the host: not recordable
     gc = copy.deepcopy(generation_config if generation_config is not None else model.generation_config)
     gc.update(**{k: v for k, v in kwargs.items() if k not in ("input_ids", "attention_mask", "streamer")})
     plain = (not gc.do_sample and (gc.num_beams or 1) == 1 and (getattr(gc, "num_beam_groups", 1) or 1) == 1
@@ -319,7 +322,14 @@ def generate_greedy_graph(self, inputs=None, generation_config=None, **kwargs):
     B, prompt_len = input_ids.shape
     dev = input_ids.device
     with torch.cuda.device(dev):
-        g = get_decode_graph(self, B, prompt_len + max_new)
+        failed = self.__dict__.setdefault("_b200_decode_graph_failed", {})
+        try:
+            g = None if B in failed else get_decode_graph(self, B, prompt_len + max_new)
+        except RuntimeError as e:                            # a step that cannot be recorded at this batch size (a mixture of
+            failed[B] = str(e)                               # experts sorts several tokens on the host): transformers' loop serves it
+            g = None
+        if g is None:
+            return self._hf_generate(inputs, generation_config=generation_config, **kwargs)
         if streamer is not None:
             streamer.put(input_ids.cpu())
         torch.cuda.synchronize(dev)

@@ -225,9 +225,11 @@ def softmax_attention(q, k, v, B, S, heads, held, shift, pad, window, scale, out
                       "softmax_attention: unexpected layout")
     if out is None:
         out = torch.empty(B * S, heads * vdim, dtype=q.dtype, device=q.device)
+    need = native.lib().mixers_softmax_attention_workspace(native.dtype_code(q.dtype), B, S, heads, kv_heads, dim, vdim) if tensor_cores else 0
+    ws = torch.empty(need, dtype=torch.float32, device=q.device) if need else None
     native.call("mixers_softmax_attention", native.dtype_code(q.dtype), native.ptr(q), q.stride(0), native.ptr(k), k.stride(0), k.stride(1), k.stride(2),
                 native.ptr(v), v.stride(0), v.stride(1), v.stride(2), B, S, heads, kv_heads, dim, vdim, int(held), int(shift), native.ptr(pad),
-                int(window), float(scale), native.ptr(out), out.stride(0), int(out_col), native.ptr(dyn), int(bool(tensor_cores)),
+                int(window), float(scale), native.ptr(out), out.stride(0), int(out_col), native.ptr(dyn), int(bool(tensor_cores)), native.ptr(ws),
                 native.stream(q.device))
     return out
 

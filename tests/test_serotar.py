@@ -383,6 +383,61 @@ def test_one_outstanding_key_decides(mixers, cuda_device, dtype, S):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("S,held,H,G,D,Dv,window,latent", [(1, 700, 16, 1, 512, 512, 0, True), (1, 63, 8, 2, 64, 128, 0, False),
+                                                             (3, 130, 4, 1, 32, 256, 0, False), (16, 200, 6, 1, 128, 128, 0, True),
+                                                             (2, 300, 8, 2, 48, 128, 90, False), (1, 0, 4, 1, 256, 256, 0, True)])
+def test_softmax_attention_shared_heads(mixers, cuda_device, dtype, S, held, H, G, D, Dv, window, latent):
+    """few new tokens whose heads share keys and values: one pass over the keys for all heads, key ranges split over blocks and
+    merged; ``latent``: keys and values are the same tensor (a latent cache read as one shared head)"""
+    g = torch.Generator().manual_seed(S * 7 + held)
+    B = 3
+    q, k, v = _attention_case(g, B, S, held, H, G, D, Dv, dtype, cuda_device, extra=5)
+    q = q * 0.5
+    if latent:
+        v = k
+    pads = [0, min(held + S - 1, 41), 0]
+    pad = torch.tensor(pads, dtype=torch.int32, device=cuda_device)
+    scale = 1.5 / D ** 0.5
+    from ipex_llm_b200.ggml.model import mixers_cpp
+    assert mixers_cpp.lib().mixers_softmax_attention_workspace(mixers_cpp.dtype_code(dtype), B, S, H, G, D, Dv) > 0
+    got = mixers.softmax_attention(q, k, v, B, S, H, held, 0, pad, window, scale, tensor_cores=True)
+    same = mixers.softmax_attention(q, k, v, B, S, H, held, 0, pad, window, scale, tensor_cores=False)
+    want = _attention_want(q, k, v, B, S, held, H, scale, window, pads)
+    assert (got.cpu().to(F64) - want).abs().max() < 0.02 and (same.cpu().to(F64) - want).abs().max() < 0.02
+    assert (got.float() - same.float()).abs().max() < 0.012
+    # the length read from the device, as a replayed step does
+    dyn = torch.tensor([held], dtype=torch.int32, device=cuda_device)
+    again = mixers.softmax_attention(q, k, v, B, S, H, 0, 0, pad, window, scale, dyn=dyn, tensor_cores=True)
+    assert torch.equal(again, got)
+
+
+@pytest.mark.gpu
+def test_one_outstanding_key_decides_for_shared_heads(mixers, cuda_device):
+    """the same proof for the kernel that splits the keys over blocks: a far key, the borders of its 64-key tiles and of its
+    key ranges, a window's two sides, padding, the future"""
+    g = torch.Generator().manual_seed(12)
+    H, D, L = 8, 128, 1500
+    base = torch.randn(1, L + 8, 1, D, generator=g) * 0.1
+    spike = torch.zeros(D)
+    spike[5] = 3.0
+    q = (torch.randn(1, H * D, generator=g) * 0.1 + spike.repeat(H)[None] * 8).to(torch.bfloat16).to(cuda_device)      # q . spike = 72
+
+    def run(at, window=0, first=0):
+        c = base.clone()
+        c[0, at, 0] = spike
+        c = c.to(torch.bfloat16).to(cuda_device)
+        out = mixers.softmax_attention(q, c, c, 1, 1, H, L - 1, 0, torch.tensor([first], dtype=torch.int32, device=cuda_device), window, 1.0)
+        return out.float().cpu().view(H, D)
+
+    for at in (0, 63, 64, 127, 128, 191, 192, 700, 1023, 1024, L - 2, L - 1):
+        assert (run(at) - spike).abs().max() < 0.05, at
+    assert (run(L - 200, window=200) - spike).abs().max() < 0.05 and (run(L - 201, window=200) - spike).abs().max() > 1.0
+    assert (run(9, first=10) - spike).abs().max() > 1.0 and (run(10, first=10) - spike).abs().max() < 0.05
+    assert (run(L) - spike).abs().max() > 1.0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_out,groups,keep,top,shift", [(9, 3, 2, 3, 0.0), (12, 4, 2, 3, -3.0), (8, 1, 1, 8, 0.0), (10, 10, 3, 3, 0.0),
                                                            (64, 8, 4, 6, -1.0), (5, 1, 1, 1, 0.0), (6, 3, 1, 2, 0.0)])
