@@ -371,10 +371,10 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
     constexpr int vdim = 64 * NT;
     extern __shared__ __align__(16) unsigned char sh_raw[];
     const int kstride = dim + 8, vstride = vdim + 8;
+    const int stage_elems = SH_KEYS * kstride + (SAME ? 0 : SH_KEYS * vstride);
     T* Qs = reinterpret_cast<T*>(sh_raw);                   // [16][kstride]
-    T* Ks = Qs + 16 * kstride;                              // [SH_KEYS][kstride]
-    T* Vs = SAME ? Ks : Ks + SH_KEYS * kstride;             // [SH_KEYS][vstride]
-    float* Ss = reinterpret_cast<float*>(Ks + SH_KEYS * kstride + (SAME ? 0 : SH_KEYS * vstride));      // [16][SH_SSTRIDE]
+    T* Kst = Qs + 16 * kstride;                             // two stages of [SH_KEYS][kstride] keys (+ [SH_KEYS][vstride] values)
+    float* Ss = reinterpret_cast<float*>(Kst + 2 * stage_elems);                                         // [16][SH_SSTRIDE]
     int* row_c = reinterpret_cast<int*>(Ss + 16 * SH_SSTRIDE);                                           // [16] newest visible key, -1: none
     int* row_lo = row_c + 16;                                                                            // [16] oldest visible key
     if (dyn) held = dyn[0];
@@ -395,15 +395,6 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
         }
         row_c[tid] = c;
         row_lo[tid] = lo;
-    }
-    // the queries of this tile's rows, zeros for rows that do not exist
-    const int qchunks = dim >> 3;
-    for (int id = tid; id < 16 * qchunks; id += 256) {
-        const int i = id / qchunks, cch = id - i * qchunks;
-        const int r = tile * 16 + i;
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((long)b * S + r / gs) * q_ld + (long)(g * gs + r % gs) * dim + cch * 8);
-        *reinterpret_cast<uint4*>(Qs + i * kstride + cch * 8) = val;
     }
     __syncthreads();
     int lo_all = 0x7fffffff, hi_all = -1;
@@ -431,21 +422,48 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
     const T* vbase = v + b * v_bs + g * v_hs;
     const int kchunks = dim >> 3, vchunks = vdim >> 3, kdn = dim >> 4;
 
-    for (int jt = j_lo; jt <= j_hi; jt += SH_KEYS) {
-        __syncthreads();                                    // the previous tile (and its scores) has been consumed
+    // two stages of key (and value) tiles: the next tile's copies (cp.async, 16 bytes each) fly while this one is multiplied
+    auto load_tile = [&](int stage, int jt) {
+        T* kd_ = Kst + stage * stage_elems;
         for (int id = tid; id < SH_KEYS * kchunks; id += 256) {
             const int r = id / kchunks, cch = id - r * kchunks;
             const int j = jt + r <= j_hi ? jt + r : j_hi;   // rows past the end repeat the last one (their weights are zero)
-            *reinterpret_cast<uint4*>(Ks + r * kstride + cch * 8) = *reinterpret_cast<const uint4*>(kbase + j * k_ps + cch * 8);
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(kd_ + r * kstride + cch * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(kbase + j * k_ps + cch * 8));
         }
         if (!SAME) {
+            T* vd_ = kd_ + SH_KEYS * kstride;
             for (int id = tid; id < SH_KEYS * vchunks; id += 256) {
                 const int r = id / vchunks, cch = id - r * vchunks;
                 const int j = jt + r <= j_hi ? jt + r : j_hi;
-                *reinterpret_cast<uint4*>(Vs + r * vstride + cch * 8) = *reinterpret_cast<const uint4*>(vbase + j * v_ps + cch * 8);
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(vd_ + r * vstride + cch * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(vbase + j * v_ps + cch * 8));
             }
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    if (j_lo <= j_hi) load_tile(0, j_lo);
+    {   // the queries of this tile's rows, zeros for rows that do not exist (while the first keys are on their way)
+        const int qchunks = dim >> 3;
+        for (int id = tid; id < 16 * qchunks; id += 256) {
+            const int i = id / qchunks, cch = id - i * qchunks;
+            const int r = tile * 16 + i;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((long)b * S + r / gs) * q_ld + (long)(g * gs + r % gs) * dim + cch * 8);
+            *reinterpret_cast<uint4*>(Qs + i * kstride + cch * 8) = val;
+        }
+    }
+    int stage = 0;
+    for (int jt = j_lo; jt <= j_hi; jt += SH_KEYS, stage ^= 1) {
+        if (jt + SH_KEYS <= j_hi) {
+            load_tile(stage ^ 1, jt + SH_KEYS);            // its stage was consumed before the barrier that ended the last turn
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();                                    // this tile (and, the first time, the queries) is there for every thread
+        const T* Ks = Kst + stage * stage_elems;
+        const T* Vs = SAME ? Ks : Ks + SH_KEYS * kstride;
         {   // scores of keys 8 wid .. 8 wid + 7 for the 16 rows
             float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             const T* qrow = Qs + gr * kstride + 2 * tq;
@@ -527,6 +545,7 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
                 SaMma<T>::mma(oacc[2 * np + 1], pl, v2, v3);
             }
         }
+        __syncthreads();                                    // tile and scores consumed: the next turn overwrites this stage
     }
     // this range's share: per row the maximum, the sum, and the weighted values
     float* base = ws + (((long)b * gridDim.y + blockIdx.y) * splits + split) * (16L * (vdim + 2));
@@ -546,7 +565,7 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
 // grid (16 x 16-row tiles x kv heads, batch): one block per row adds up the key ranges' shares.  Warp 0 turns the ranges'
 // maxima into factors; then every thread owns two neighbouring columns and reads them from all ranges (independent loads).
 template <typename T>
-__global__ void __launch_bounds__(128) shared_head_merge_kernel(const float* __restrict__ ws, int S, int heads, int kv_heads, int vdim, int splits,
+__global__ void __launch_bounds__(256) shared_head_merge_kernel(const float* __restrict__ ws, int S, int heads, int kv_heads, int vdim, int splits,
                                                                 int tiles, T* __restrict__ out, long ld_out, int out_col) {
     __shared__ float factor[SH_MAX_SPLITS];
     __shared__ float inv_total;
@@ -568,10 +587,11 @@ __global__ void __launch_bounds__(128) shared_head_merge_kernel(const float* __r
     }
     __syncthreads();
     T* dst = out + ((long)b * S + r / gs) * ld_out + out_col + (long)(g * gs + r % gs) * vdim;
-    for (int col = 2 * threadIdx.x; col < vdim; col += 256) {
+    for (int col = 2 * threadIdx.x; col < vdim; col += 512) {
         float sx = 0.0f, sy = 0.0f;
 #pragma unroll 8
         for (int s = 0; s < splits; ++s) {
+            if (factor[s] == 0.0f) continue;                // an empty range (the same for the whole block)
             const float2 o = *reinterpret_cast<const float2*>(base + s * sstride + 2 + col);
             sx += o.x * factor[s];
             sy += o.y * factor[s];
@@ -584,13 +604,18 @@ __global__ void __launch_bounds__(128) shared_head_merge_kernel(const float* __r
 static int shared_head_splits(int B, int S, int heads, int kv_heads) {
     const int tiles = (S * (heads / kv_heads) + 15) / 16;
     long blocks = (long)B * kv_heads * tiles;
-    long s = (2L * 148 + blocks - 1) / blocks;
+    long s = (148 + blocks - 1) / blocks;                   // one block per SM (two stages of key tiles fill its shared memory)
     return (int)(s < 1 ? 1 : (s > SH_MAX_SPLITS ? SH_MAX_SPLITS : s));
 }
 
 static bool shared_head_ok(int dtype, int S, int heads, int kv_heads, int dim, int vdim) {
     return dtype != 0 && kv_heads >= 1 && heads % kv_heads == 0 && heads / kv_heads >= 4 && S <= 16 && dim % 16 == 0 && dim <= 512 &&
            (vdim == 128 || vdim == 256 || vdim == 512);
+}
+
+static size_t shared_head_smem(int dim, int vdim, bool same) {
+    return (size_t)(16 + 2 * SH_KEYS) * (dim + 8) * 2 + (same ? 0 : 2 * (size_t)SH_KEYS * (vdim + 8) * 2) + 16 * SH_SSTRIDE * sizeof(float) +
+           32 * sizeof(int);
 }
 
 template <typename T, int NT>
@@ -600,8 +625,7 @@ static int launch_shared_head(const void* q, long q_ld, const void* k, long k_bs
     const int vdim = 64 * NT;
     const int tiles = (S * (heads / kv_heads) + 15) / 16, splits = shared_head_splits(B, S, heads, kv_heads);
     const bool same = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
-    size_t smem = (size_t)(16 + SH_KEYS) * (dim + 8) * sizeof(T) + (same ? 0 : (size_t)SH_KEYS * (vdim + 8) * sizeof(T)) +
-                  16 * SH_SSTRIDE * sizeof(float) + 32 * sizeof(int);
+    const size_t smem = shared_head_smem(dim, vdim, same);
     dim3 grid(splits, tiles * kv_heads, B);
     cudaError_t err;
     if (same) {
@@ -616,7 +640,7 @@ static int launch_shared_head(const void* q, long q_ld, const void* k, long k_bs
                                         shift, pad, window, scale, ws, splits, tiles, dyn);
     }
     if ((err = cudaGetLastError()) != cudaSuccess) return (int)err;
-    shared_head_merge_kernel<T><<<dim3(16 * tiles * kv_heads, B), 128, 0, stream>>>(ws, S, heads, kv_heads, vdim, splits, tiles, (T*)out, ld_out, out_col);
+    shared_head_merge_kernel<T><<<dim3(16 * tiles * kv_heads, B), 256, 0, stream>>>(ws, S, heads, kv_heads, vdim, splits, tiles, (T*)out, ld_out, out_col);
     return mixers_status();
 }
 
@@ -672,8 +696,9 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, con
     auto mult8 = [](long s) { return (s & 7) == 0; };
     const bool rows16 = esz == 2 && mult8(k_bs) && mult8(k_ps) && mult8(k_hs) && mult8(v_bs) && mult8(v_ps) && mult8(v_hs) &&
                         ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && (dim & 7) == 0;
+    const bool same_kv = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
     if (allow_tensor_cores && ws && rows16 && shared_head_ok(dtype, S, heads, kv_heads, dim, vdim) && (q_ld & 7) == 0 && ((uintptr_t)q & 15) == 0 &&
-        (ld_out & 1) == 0 && (out_col & 1) == 0) {
+        (ld_out & 1) == 0 && (out_col & 1) == 0 && shared_head_smem(dim, vdim, same_kv) <= 227 * 1024) {
 #define SH_ARGS q, q_ld, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, scale, out, ld_out, out_col, dyn, ws, stream
         if (dtype == 1) return vdim == 128 ? launch_shared_head<__nv_bfloat16, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__nv_bfloat16, 4>(SH_ARGS)
                                                                                                        : launch_shared_head<__nv_bfloat16, 8>(SH_ARGS);
