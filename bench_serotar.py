@@ -144,7 +144,8 @@ def kernel_table(dev, dtype, peaks, timer, serotar, mixtral):
                 real = idx[:n][idx[:n] < EXPERTS]
                 distinct, pairs = int(real.unique().numel()), int(real.numel())
                 add(f"moe_small ({n} rows, {pairs} expert calls on {distinct} experts)", phase,
-                    timer(lambda: ops.moe_small(h[:n], idx[:n], wgt[:n], tables[0], tables[1], EXPERT_FF, EXPERTS, EXPERTS + IDENTITY, None)),
+                    timer(lambda: ops.moe_small(h[:n], idx[:n], wgt[:n], tables[0], tables[1], EXPERT_FF, EXPERTS, EXPERTS + IDENTITY, None,
+                                                ffs=tables[2])),
                     bytes_=distinct * 3 * EXPERT_FF * WIDTH * es, like="lowbit_moe (moe_forward_vec)")
         else:
             rows_ = rnd(N * TOP, WIDTH)

@@ -111,7 +111,7 @@ int mixers_latent_prepare(int dtype, const void* proj, int B, int S, int ld, int
                           int kv_rank, const void* c_w, float eps, void* cq_out, void* store, int cap, int held, int shift,
                           const int32_t* pad, const int32_t* dyn, mixers_stream_t stream);
 
-/* Causal softmax attention of S new tokens per row.  q: head h of token n at q + n * q_ld + h * dim.  Key (value) of storage
+/* Causal softmax attention of S new tokens per row.  q: head h of token n at q + n * q_ld + h * q_hs.  Key (value) of storage
  * index j, row b, kv head g at k + b * k_bs + j * k_ps + g * k_hs (strides in elements).  The query at storage index c = held
  * + t sees the keys j <= c of its row that are not padding (j + shift >= pad[b]) and, if window > 0, c - j < window.  Scores
  * (q . k) * scale and the softmax weights are 32-bit.  out[n, out_col + h * vdim + :] in dtype (zeros for padding queries).
@@ -119,7 +119,7 @@ int mixers_latent_prepare(int dtype, const void* proj, int B, int S, int ld, int
  * multiples of 16, <= 256); for S <= 16 and at least 4 query heads per kv head one pass over the keys for all heads of a
  * group, the keys split over blocks (dim a multiple of 16, <= 512; vdim 128, 256 or 512), which needs `ws`:
  * mixers_softmax_attention_workspace(...) floats (0: these sizes never take that kernel).  dyn as above. */
-int mixers_softmax_attention(int dtype, const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
+int mixers_softmax_attention(int dtype, const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                              long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
                              int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
                              const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream);
@@ -133,13 +133,14 @@ long mixers_softmax_attention_workspace(int dtype, int B, int S, int heads, int 
 int mixers_grouped_router(int dtype, const void* h, long n_rows, int width, const void* router, const void* correction, int n_out,
                           int groups, int keep, int top, int32_t* idx_out, float* w_out, mixers_stream_t stream);
 
-/* The chosen experts of a few tokens without host work.  gate_up[e] / down[e]: addresses of expert e's [2 ff, width] (gate rows,
- * then up rows) and [width, ff] matrices in dtype.  act: scratch dtype [n_rows, top, ff].  y float [n_rows, width] =
- * sum_k w_k * down_e (silu(gate_e h) * (up_e h)) for chosen e < n_experts, w_k * h for n_experts <= e < n_out, + shared_out
- * (dtype [n_rows, width], may be null). */
+/* The chosen experts of a few tokens without host work.  gate_up[e] / down[e]: addresses of expert e's [2 ff_e, width] (gate rows,
+ * then up rows) and [width, ff_e] matrices in dtype; ffs[e] = ff_e (null: `ff` for all; `ff` is the largest).  always_on != 0:
+ * table entry n_experts is an expert that every token runs with weight 1 (a shared expert).  act: scratch dtype [n_rows, top +
+ * (always_on ? 1 : 0), ff].  y float [n_rows, width] = sum_k w_k * down_e (silu(gate_e h) * (up_e h)) for chosen e < n_experts,
+ * w_k * h for n_experts <= e < n_out, + the always-on expert, + shared_out (dtype [n_rows, width], may be null). */
 int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, int top, int n_experts, int n_out, const int32_t* idx,
-                     const float* wgt, const int64_t* gate_up, const int64_t* down, const void* shared_out, void* act, float* y,
-                     mixers_stream_t stream);
+                     const float* wgt, const int64_t* gate_up, const int64_t* down, const int32_t* ffs, int always_on,
+                     const void* shared_out, void* act, float* y, mixers_stream_t stream);
 
 /* y float [n_rows, width] = sum_k w[n, k] * rows[pos[n, k], :] for chosen e < n_experts, w * h[n, :] for identity experts,
  * + shared_out; rows: dtype [*, width], the experts' outputs on rows sorted by expert. */

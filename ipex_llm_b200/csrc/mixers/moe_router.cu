@@ -2,7 +2,7 @@
 //   grouped_router: 32-bit router logits, softmax over all outputs, a correction that enters the ranking but not the
 //     weights, consecutive outputs ranked as groups first (only the leading groups stay eligible), then top-k among the
 //     eligible; weights = the winners' softmax scores;
-//   moe_small_gate_up / moe_small_down: the chosen experts of a few tokens straight from the experts' weight matrices (device
+//   moe_small_up / moe_small_down: the chosen experts of a few tokens straight from the experts' weight matrices (device
 //     tables of addresses), nothing on the host between router and result: the path of decoding and of a recorded step;
 //   moe_combine: the weighted sum of expert outputs that were computed expert by expert on sorted rows (many tokens).
 // Outputs numbered >= n_experts are identity experts: their output is the token's input itself.
@@ -107,42 +107,51 @@ __global__ void __launch_bounds__(ROUTER_WARPS * 32) grouped_router_kernel(
     }
 }
 
-// grid (ceil(ff / 8), n_rows * top), 8 warps a block, one warp per row of the chosen expert's gate and up matrices.
-// gate_up[e]: address of expert e's [2 ff, width] matrix (gate rows first).  act[n, k, j] = silu(gate_j . h) * (up_j . h)
+// The chosen experts of a few tokens.  Every token has `slots` expert calls: its `top` choices and, if there is an always-on
+// expert, that one as slot number `top` (table entry n_experts, weight 1).  gate_up[e]: address of expert e's [2 ff_e, width]
+// matrix (gate rows first), down[e]: [width, ff_e]; ffs[e] = ff_e (null: `ff` for all).  act: [n_rows, slots, ff] scratch.
+// grid (ceil(ff / 8), n_rows * slots), 8 warps a block, one warp per row pair of the gate and up matrices:
+// act[n, k, j] = silu(gate_j . h) * (up_j . h)
 template <typename T>
 __global__ void __launch_bounds__(256) moe_small_up_kernel(const T* __restrict__ h, const int32_t* __restrict__ idx, const int64_t* __restrict__ gate_up,
-                                                           int width, int ff, int top, int n_experts, T* __restrict__ act) {
+                                                           const int32_t* __restrict__ ffs, int width, int ff, int top, int slots, int n_experts,
+                                                           T* __restrict__ act) {
     const int lane = threadIdx.x & 31;
     const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
     const long nk = blockIdx.y;
-    const int e = idx[nk];
-    if (j >= ff || e >= n_experts) return;
-    const long n = nk / top;
+    const long n = nk / slots;
+    const int k = (int)(nk - n * slots);
+    const int e = k < top ? idx[n * top + k] : n_experts;
+    if (k < top && e >= n_experts) return;                  // an identity expert, or nothing chosen
+    const int ff_e = ffs ? ffs[e] : ff;
+    if (j >= ff_e) return;
     const T* w = reinterpret_cast<const T*>(gate_up[e]);
     const T* hr = h + n * width;
     // the products leave the matrix unit of the many-token path rounded to the model's type: the same rounding here
     const float g = to_f(from_f<T>(warp_dot(w + (long)j * width, hr, width, lane)));
-    const float u = to_f(from_f<T>(warp_dot(w + ((long)ff + j) * width, hr, width, lane)));
+    const float u = to_f(from_f<T>(warp_dot(w + ((long)ff_e + j) * width, hr, width, lane)));
     if (lane == 0) act[nk * ff + j] = from_f<T>(silu_f(g) * u);
 }
 
-// grid (ceil(width / 8), n_rows): one warp per output column.  y[n, c] = sum_k w[n, k] * (down[e_k][c, :] . act[n, k, :])
-// (identity experts: w * h[n, c]) + shared[n, c]
+// grid (ceil(width / 8), n_rows): one warp per output column.  y[n, c] = sum over the token's slots of w * (down_e[c, :] . act)
+// (identity experts: w * h[n, c]) + shared_out[n, c]
 template <typename T>
 __global__ void __launch_bounds__(256) moe_small_down_kernel(const T* __restrict__ act, const int32_t* __restrict__ idx, const float* __restrict__ wgt,
-                                                             const int64_t* __restrict__ down, const T* __restrict__ h, const T* __restrict__ shared_out,
-                                                             int width, int ff, int top, int n_experts, int n_out, float* __restrict__ y) {
+                                                             const int64_t* __restrict__ down, const int32_t* __restrict__ ffs, const T* __restrict__ h,
+                                                             const T* __restrict__ shared_out, int width, int ff, int top, int slots, int n_experts,
+                                                             int n_out, float* __restrict__ y) {
     const int lane = threadIdx.x & 31;
     const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
     const long n = blockIdx.y;
     if (c >= width) return;
     float sum = 0.0f;
-    for (int k = 0; k < top; ++k) {
-        const int e = idx[n * top + k];
-        const float w = wgt[n * top + k];
-        if (e < n_experts) {
+    for (int k = 0; k < slots; ++k) {
+        const int e = k < top ? idx[n * top + k] : n_experts;
+        const float w = k < top ? wgt[n * top + k] : 1.0f;
+        if (k == top || e < n_experts) {
+            const int ff_e = ffs ? ffs[e] : ff;
             const T* wd = reinterpret_cast<const T*>(down[e]);
-            sum += w * to_f(from_f<T>(warp_dot(wd + (long)c * ff, act + (n * top + k) * ff, ff, lane)));
+            sum += w * to_f(from_f<T>(warp_dot(wd + (long)c * ff_e, act + (n * slots + k) * ff, ff_e, lane)));
         } else if (e < n_out) {
             sum += w * to_f(h[n * width + c]);
         }
@@ -184,17 +193,19 @@ extern "C" int mixers_grouped_router(int dtype, const void* h, long n_rows, int 
 }
 
 extern "C" int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, int top, int n_experts, int n_out, const int32_t* idx,
-                                const float* wgt, const int64_t* gate_up, const int64_t* down, const void* shared_out, void* act, float* y,
-                                mixers_stream_t stream) {
+                                const float* wgt, const int64_t* gate_up, const int64_t* down, const int32_t* ffs, int always_on,
+                                const void* shared_out, void* act, float* y, mixers_stream_t stream) {
     if (n_rows <= 0) return 0;
-    if (n_rows * top > 65535 || n_rows > 65535) return (int)cudaErrorInvalidValue;
-    if (n_experts > 0 && ff > 0) {
-        dim3 g1((ff + 7) / 8, (unsigned)(n_rows * top));
-        MIXERS_DISPATCH(dtype, moe_small_up_kernel<T><<<g1, 256, 0, (cudaStream_t)stream>>>((const T*)h, idx, gate_up, width, ff, top, n_experts, (T*)act));
+    const int slots = top + (always_on ? 1 : 0);
+    if (n_rows * slots > 65535 || n_rows > 65535) return (int)cudaErrorInvalidValue;
+    if ((n_experts > 0 || always_on) && ff > 0) {
+        dim3 g1((ff + 7) / 8, (unsigned)(n_rows * slots));
+        MIXERS_DISPATCH(dtype, moe_small_up_kernel<T><<<g1, 256, 0, (cudaStream_t)stream>>>((const T*)h, idx, gate_up, ffs, width, ff, top, slots, n_experts,
+                                                                                          (T*)act));
     }
     dim3 g2((width + 7) / 8, (unsigned)n_rows);
     MIXERS_DISPATCH(dtype, moe_small_down_kernel<T><<<g2, 256, 0, (cudaStream_t)stream>>>(
-        (const T*)act, idx, wgt, down, (const T*)h, (const T*)shared_out, width, ff, top, n_experts, n_out, y));
+        (const T*)act, idx, wgt, down, ffs, (const T*)h, (const T*)shared_out, width, ff, top, slots, n_experts, n_out, y));
     return mixers_status();
 }
 

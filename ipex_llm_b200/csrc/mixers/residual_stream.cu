@@ -83,6 +83,59 @@ __global__ void rms_residual_kernel(float* __restrict__ x, const TY* __restrict_
     }
 }
 
+// the same with a row's elements held in registers (rows up to 8 x blockDim wide): every global load -- y, x, the vector, the
+// earlier streams of the depth average -- is issued before the row's sum is reduced, so a lone row (a decoding step) pays one
+// round trip to memory instead of one per loop turn
+constexpr int RR_MAXC = 8;
+template <typename T, typename TY>
+__global__ void rms_residual_cached_kernel(float* __restrict__ x, const TY* __restrict__ y, const T* __restrict__ gain, const T* __restrict__ vec,
+                                           float eps, int width, float* __restrict__ stack, long stack_stride, int index,
+                                           const T* __restrict__ coef, T* __restrict__ h) {
+    __shared__ float red[32];
+    const long base = (long)blockIdx.x * width;
+    float yv[RR_MAXC], xv[RR_MAXC], vv[RR_MAXC], av[RR_MAXC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < RR_MAXC; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        yv[k] = 0.0f; xv[k] = 0.0f; vv[k] = 1.0f; av[k] = 0.0f;
+        if (c < width) {
+            yv[k] = to_f(y[base + c]);
+            xv[k] = x[base + c];
+            if (vec) vv[k] = to_f(vec[c]);
+        }
+        ss += yv[k] * yv[k];
+    }
+    if (coef) {
+        for (int j = 0; j < index; ++j) {
+            const float cj = to_f(coef[j]);
+            const float* sj = stack + j * stack_stride + base;
+#pragma unroll
+            for (int k = 0; k < RR_MAXC; ++k) {
+                const int c = threadIdx.x + k * blockDim.x;
+                if (c < width) av[k] += cj * sj[c];
+            }
+        }
+    }
+    ss = block_sum(ss, red);
+    float f = 1.0f / sqrtf(ss / (float)width + eps);
+    if (gain) f *= to_f(gain[0]);
+    const float last = coef ? to_f(coef[index]) : 1.0f;
+#pragma unroll
+    for (int k = 0; k < RR_MAXC; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < width) {
+            float v = xv[k] + yv[k] * f * vv[k];
+            if (stack) {
+                stack[index * stack_stride + base + c] = v;
+                if (coef) v = av[k] + last * v;
+            }
+            x[base + c] = v;
+            if (h) h[base + c] = from_f<T>(v);
+        }
+    }
+}
+
 // one block per row: out = x / rms(x) * gain * vec
 template <typename T>
 __global__ void rms_norm_rows_kernel(const float* __restrict__ x, const T* __restrict__ gain, const T* __restrict__ vec, float eps, int width,
@@ -152,6 +205,19 @@ extern "C" int mixers_rms_residual(int dtype, float* x, long n_rows, int width, 
                                    float eps, float* stack, long stack_stride, int index, const void* coef, void* h, mixers_stream_t stream) {
     if (n_rows <= 0) return 0;
     if (coef && !stack) return (int)cudaErrorInvalidValue;
+    // many rows keep the memory system busy by themselves, and the depth average then streams better from the plain loop
+    if (width <= RR_MAXC * 1024 && (n_rows <= 1024 || !coef)) {
+        int cached = ((width + RR_MAXC - 1) / RR_MAXC + 31) / 32 * 32;
+        if (cached < 64) cached = 64;
+        if (y_is_float) {
+            MIXERS_DISPATCH(dtype, rms_residual_cached_kernel<T, float><<<(unsigned)n_rows, cached, 0, (cudaStream_t)stream>>>(
+                x, (const float*)y, (const T*)gain, (const T*)vec, eps, width, stack, stack_stride, index, (const T*)coef, (T*)h));
+        } else {
+            MIXERS_DISPATCH(dtype, rms_residual_cached_kernel<T, T><<<(unsigned)n_rows, cached, 0, (cudaStream_t)stream>>>(
+                x, (const T*)y, (const T*)gain, (const T*)vec, eps, width, stack, stack_stride, index, (const T*)coef, (T*)h));
+        }
+        return mixers_status();
+    }
     const int threads = width >= 1024 ? 256 : 128;
     if (y_is_float) {
         MIXERS_DISPATCH(dtype, rms_residual_kernel<T, float><<<(unsigned)n_rows, threads, 0, (cudaStream_t)stream>>>(

@@ -9,18 +9,18 @@
 #include "mixers_common.cuh"
 #include <math.h>
 
-// one warp per (token, segment): segment 0 = query latent, 1 = key/value latent
+// one block of 128 threads per (token, segment): segment 0 = query latent, 1 = key/value latent.  Segments up to 1024 wide are
+// held in registers (one round of loads); wider ones are read twice.
+constexpr int LP_THREADS = 128, LP_MAXC = 8;
 template <typename T>
-__global__ void latent_prepare_kernel(const T* __restrict__ proj, int B, int S, int ld, int off_q, int q_rank, const T* __restrict__ q_w,
-                                      int off_c, int kv_rank, const T* __restrict__ c_w, float eps, T* __restrict__ cq_out,
-                                      T* __restrict__ store, int cap, int held, int shift, const int32_t* __restrict__ pad,
-                                      const int32_t* __restrict__ dyn) {
+__global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(
+        const T* __restrict__ proj, int B, int S, int ld, int off_q, int q_rank, const T* __restrict__ q_w, int off_c, int kv_rank,
+        const T* __restrict__ c_w, float eps, T* __restrict__ cq_out, T* __restrict__ store, int cap, int held, int shift,
+        const int32_t* __restrict__ pad, const int32_t* __restrict__ dyn) {
+    __shared__ float red[LP_THREADS / 32];
     if (dyn) held = dyn[0];
-    long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (warp >= 2L * B * S) return;
-    const long n = warp >> 1;
-    const int seg = (int)(warp & 1);
+    const long n = blockIdx.x >> 1;
+    const int seg = blockIdx.x & 1;
     const int b = (int)(n / S), t = (int)(n - (long)b * S);
     const bool real = held + t + shift - pad[b] >= 0;       // padding slots hold zeros
     const int width = seg ? kv_rank : q_rank;
@@ -28,11 +28,36 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, int B, int S, 
     const T* src = proj + n * (long)ld + (seg ? off_c : off_q);
     const T* w = seg ? c_w : q_w;
     T* dst = seg ? store + ((long)b * cap + held + t) * kv_rank : cq_out + n * (long)q_rank;
+    const bool cached = width <= LP_MAXC * LP_THREADS;
+    float sv[LP_MAXC], wv[LP_MAXC];
     float ss = 0.0f;
-    for (int c = lane; c < width; c += 32) { float v = to_f(src[c]); ss += v * v; }
+    if (cached) {
+#pragma unroll
+        for (int k = 0; k < LP_MAXC; ++k) {
+            const int c = threadIdx.x + k * LP_THREADS;
+            sv[k] = c < width ? to_f(src[c]) : 0.0f;
+            wv[k] = c < width ? to_f(w[c]) : 0.0f;
+            ss += sv[k] * sv[k];
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += LP_THREADS) { float v = to_f(src[c]); ss += v * v; }
+    }
     ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int c = lane; c < width; c += 32) dst[c] = from_f<T>(real ? to_f(src[c]) * inv * to_f(w[c]) : 0.0f);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LP_THREADS / 32; ++i) ss += red[i];
+    const float inv = real ? 1.0f / sqrtf(ss / (float)width + eps) : 0.0f;
+    if (cached) {
+#pragma unroll
+        for (int k = 0; k < LP_MAXC; ++k) {
+            const int c = threadIdx.x + k * LP_THREADS;
+            if (c < width) dst[c] = from_f<T>(sv[k] * inv * wv[k]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += LP_THREADS) dst[c] = from_f<T>(to_f(src[c]) * inv * to_f(w[c]));
+    }
 }
 
 // ---- the general kernel: any sizes and strides, any dtype, 32-bit arithmetic throughout (float32 models, decoding, short
@@ -51,7 +76,7 @@ __device__ __forceinline__ float dot_strided(const float* __restrict__ qs, const
 
 template <typename T>
 __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
-        const T* __restrict__ q, long q_ld, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
+        const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
         long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
         float scale, T* __restrict__ out, long ld_out, int out_col, const int32_t* __restrict__ dyn, int aligned) {
     extern __shared__ __align__(16) float sa_sh[];          // q [dim rounded up to 4], warp maxima, warp sums, partial values
@@ -77,7 +102,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
     int lo = window > 0 ? c - window + 1 : 0;
     if (lo < first_real) lo = first_real;
     if (lo < 0) lo = 0;
-    const T* qsrc = q + n * q_ld + (long)h * dim;
+    const T* qsrc = q + n * q_ld + h * q_hs;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) qs[d] = to_f(qsrc[d]);
     __syncthreads();
     const T* kbase = k + b * k_bs + g * k_hs;
@@ -165,7 +190,7 @@ constexpr int SA_ROWS = 64, SA_KEYS = 32;
 
 template <typename T, int KDMAX, int NDMAX>                // dim <= 16 KDMAX, vdim <= 8 NDMAX; both multiples of 16
 __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
-        const T* __restrict__ q, long q_ld, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
+        const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
         long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
         float scale, T* __restrict__ out, long ld_out, int out_col) {
     extern __shared__ __align__(16) unsigned char sa_tc_sh[];
@@ -205,7 +230,7 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 if (tr[i] < S) {
-                    const T* src = q + ((long)b * S + tr[i]) * q_ld + (long)h * dim + kd * 16 + 2 * tq;
+                    const T* src = q + ((long)b * S + tr[i]) * q_ld + h * q_hs + kd * 16 + 2 * tq;
                     qa[kd][i] = *reinterpret_cast<const uint32_t*>(src);
                     qa[kd][2 + i] = *reinterpret_cast<const uint32_t*>(src + 8);
                 }
@@ -361,11 +386,11 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
 // keys, the scaled and masked scores through shared memory, then every warp forms the rows' running maxima and the weights
 // (as the sum of two 16-bit numbers, like the prompt kernel) and multiplies them into ITS 1/8 of the value columns.  Each
 // block leaves (max, sum, weighted values) of its key range in the workspace; shared_head_merge_kernel adds the ranges up.
-constexpr int SH_KEYS = 64, SH_SSTRIDE = 72, SH_MIN_CHUNK = 128, SH_MAX_SPLITS = 32;
+constexpr int SH_KEYS = 64, SH_SSTRIDE = 72, SH_MIN_CHUNK = 64, SH_MAX_SPLITS = 32;
 
 template <typename T, int NT, bool SAME>                   // vdim = 64 NT (each warp owns 8 NT value columns)
 __global__ void __launch_bounds__(256) shared_head_attention_kernel(
-        const T* __restrict__ q, long q_ld, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
+        const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
         long v_hs, int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* __restrict__ pad, int window, float scale,
         float* __restrict__ ws, int splits, int tiles, const int32_t* __restrict__ dyn) {
     constexpr int vdim = 64 * NT;
@@ -449,7 +474,7 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
             const int i = id / qchunks, cch = id - i * qchunks;
             const int r = tile * 16 + i;
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((long)b * S + r / gs) * q_ld + (long)(g * gs + r % gs) * dim + cch * 8);
+            if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((long)b * S + r / gs) * q_ld + (g * gs + r % gs) * q_hs + cch * 8);
             *reinterpret_cast<uint4*>(Qs + i * kstride + cch * 8) = val;
         }
     }
@@ -619,7 +644,7 @@ static size_t shared_head_smem(int dim, int vdim, bool same) {
 }
 
 template <typename T, int NT>
-static int launch_shared_head(const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs,
+static int launch_shared_head(const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs,
                               int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* pad, int window, float scale,
                               void* out, long ld_out, int out_col, const int32_t* dyn, float* ws, cudaStream_t stream) {
     const int vdim = 64 * NT;
@@ -631,12 +656,12 @@ static int launch_shared_head(const void* q, long q_ld, const void* k, long k_bs
     if (same) {
         auto fn = shared_head_attention_kernel<T, NT, true>;
         if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
-        fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
+        fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
                                         shift, pad, window, scale, ws, splits, tiles, dyn);
     } else {
         auto fn = shared_head_attention_kernel<T, NT, false>;
         if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
-        fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
+        fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
                                         shift, pad, window, scale, ws, splits, tiles, dyn);
     }
     if ((err = cudaGetLastError()) != cudaSuccess) return (int)err;
@@ -644,10 +669,10 @@ static int launch_shared_head(const void* q, long q_ld, const void* k, long k_bs
     return mixers_status();
 }
 
-#define SA_TC_PARAMS const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs, \
+#define SA_TC_PARAMS const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs, \
     int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* pad, int window, float scale, void* out,     \
     long ld_out, int out_col, cudaStream_t stream
-#define SA_TC_ARGS q, q_ld, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, scale, out, \
+#define SA_TC_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, scale, out, \
     ld_out, out_col, stream
 
 template <typename T, int KDMAX, int NDMAX>
@@ -659,7 +684,7 @@ static int launch_softmax_tc(SA_TC_PARAMS) {
         if (err != cudaSuccess) return (int)err;
     }
     softmax_attention_tc_kernel<T, KDMAX, NDMAX><<<grid, 128, smem, stream>>>(
-        (const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
+        (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
         scale, (T*)out, ld_out, out_col);
     return mixers_status();
 }
@@ -676,14 +701,12 @@ extern "C" int mixers_latent_prepare(int dtype, const void* proj, int B, int S, 
                                      const int32_t* pad, const int32_t* dyn, mixers_stream_t stream) {
     if (B <= 0 || S <= 0) return 0;
     if (held + S > cap) return (int)cudaErrorInvalidValue;
-    long warps = 2L * B * S;
-    int blocks = (int)((warps + 3) / 4);
-    MIXERS_DISPATCH(dtype, latent_prepare_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+    MIXERS_DISPATCH(dtype, latent_prepare_kernel<T><<<(unsigned)(2L * B * S), LP_THREADS, 0, (cudaStream_t)stream>>>(
         (const T*)proj, B, S, ld, off_q, q_rank, (const T*)q_w, off_c, kv_rank, (const T*)c_w, eps, (T*)cq_out, (T*)store, cap, held, shift, pad, dyn));
     return mixers_status();
 }
 
-extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
+extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                                         long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
                                         int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
                                         const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream_) {
@@ -697,9 +720,9 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, con
     const bool rows16 = esz == 2 && mult8(k_bs) && mult8(k_ps) && mult8(k_hs) && mult8(v_bs) && mult8(v_ps) && mult8(v_hs) &&
                         ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && (dim & 7) == 0;
     const bool same_kv = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
-    if (allow_tensor_cores && ws && rows16 && shared_head_ok(dtype, S, heads, kv_heads, dim, vdim) && (q_ld & 7) == 0 && ((uintptr_t)q & 15) == 0 &&
+    if (allow_tensor_cores && ws && rows16 && shared_head_ok(dtype, S, heads, kv_heads, dim, vdim) && (q_ld & 7) == 0 && (q_hs & 7) == 0 && ((uintptr_t)q & 15) == 0 &&
         (ld_out & 1) == 0 && (out_col & 1) == 0 && shared_head_smem(dim, vdim, same_kv) <= 227 * 1024) {
-#define SH_ARGS q, q_ld, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, scale, out, ld_out, out_col, dyn, ws, stream
+#define SH_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, scale, out, ld_out, out_col, dyn, ws, stream
         if (dtype == 1) return vdim == 128 ? launch_shared_head<__nv_bfloat16, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__nv_bfloat16, 4>(SH_ARGS)
                                                                                                        : launch_shared_head<__nv_bfloat16, 8>(SH_ARGS);
         return vdim == 128 ? launch_shared_head<__half, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__half, 4>(SH_ARGS)
@@ -707,13 +730,13 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, con
 #undef SH_ARGS
     }
     if (allow_tensor_cores && dtype != 0 && !dyn && S >= 16 && rows16 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 256 && vdim <= 256 &&
-        (q_ld & 1) == 0 && ((uintptr_t)q & 3) == 0 && (ld_out & 1) == 0 && (out_col & 1) == 0) {
+        (q_ld & 1) == 0 && (q_hs & 1) == 0 && ((uintptr_t)q & 3) == 0 && (ld_out & 1) == 0 && (out_col & 1) == 0) {
         if (dtype == 1) return softmax_tc<__nv_bfloat16>(SA_TC_ARGS);
         return softmax_tc<__half>(SA_TC_ARGS);
     }
     long items = (long)B * S * heads;
     MIXERS_DISPATCH(dtype, softmax_attention_kernel<T><<<(unsigned)items, SA_WARPS * 32, smem, stream>>>(
-        (const T*)q, q_ld, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
+        (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
         scale, (T*)out, ld_out, out_col, dyn, rows16 ? 1 : 0));
     return mixers_status();
 }

@@ -45,11 +45,11 @@ _SIGNATURES = {
     "mixers_gelu_table_mul": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_latent_prepare": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
-    "mixers_softmax_attention": [_c_int, _c_ptr, _c_long, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long] + [_c_int] * 8
+    "mixers_softmax_attention": [_c_int, _c_ptr, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long] + [_c_int] * 8
                                 + [_c_ptr, _c_int, _c_float, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "mixers_grouped_router": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
-    "mixers_moe_small": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
-                         _c_ptr],
+    "mixers_moe_small": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+                         _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_combine": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
 }
 

@@ -217,20 +217,21 @@ def latent_prepare(proj, off_q, q_rank, q_w, off_c, kv_rank, c_w, eps, store, he
 
 
 def softmax_attention(q, k, v, B, S, heads, held, shift, pad, window, scale, out=None, out_col=0, dyn=None, tensor_cores=True):
-    """q [B * S, heads * dim] (rows may be strided); k [B, L, kv_heads, dim], v [B, L, kv_heads, vdim] views (any strides with a
-    unit last one); returns out [B * S, heads * vdim] in q's dtype"""
+    """q [B * S, heads * dim], or [B * S, heads, dim] with any token and head strides; k [B, L, kv_heads, dim], v [B, L, kv_heads,
+    vdim] views (any strides with a unit last one); returns out [B * S, heads * vdim] in q's dtype"""
     kv_heads, dim, vdim = k.shape[2], k.shape[3], v.shape[3]
-    invalidInputError(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and q.shape[-1] == heads * dim and k.dtype == q.dtype
+    q_hs = q.stride(1) if q.dim() == 3 else dim
+    invalidInputError(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and q.numel() == B * S * heads * dim and k.dtype == q.dtype
                       and v.dtype == q.dtype and v.shape[2] == kv_heads and (dyn is not None or (k.shape[1] >= held + S and v.shape[1] >= held + S)),
                       "softmax_attention: unexpected layout")
     if out is None:
         out = torch.empty(B * S, heads * vdim, dtype=q.dtype, device=q.device)
     need = native.lib().mixers_softmax_attention_workspace(native.dtype_code(q.dtype), B, S, heads, kv_heads, dim, vdim) if tensor_cores else 0
     ws = torch.empty(need, dtype=torch.float32, device=q.device) if need else None
-    native.call("mixers_softmax_attention", native.dtype_code(q.dtype), native.ptr(q), q.stride(0), native.ptr(k), k.stride(0), k.stride(1), k.stride(2),
-                native.ptr(v), v.stride(0), v.stride(1), v.stride(2), B, S, heads, kv_heads, dim, vdim, int(held), int(shift), native.ptr(pad),
-                int(window), float(scale), native.ptr(out), out.stride(0), int(out_col), native.ptr(dyn), int(bool(tensor_cores)), native.ptr(ws),
-                native.stream(q.device))
+    native.call("mixers_softmax_attention", native.dtype_code(q.dtype), native.ptr(q), q.stride(0), q_hs, native.ptr(k), k.stride(0), k.stride(1),
+                k.stride(2), native.ptr(v), v.stride(0), v.stride(1), v.stride(2), B, S, heads, kv_heads, dim, vdim, int(held), int(shift),
+                native.ptr(pad), int(window), float(scale), native.ptr(out), out.stride(0), int(out_col), native.ptr(dyn), int(bool(tensor_cores)),
+                native.ptr(ws), native.stream(q.device))
     return out
 
 
@@ -247,16 +248,17 @@ def grouped_router(h, router, correction, groups, keep, top):
     return idx, wgt
 
 
-def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shared_out):
-    """fp32 [N, W]: the chosen experts of a few tokens through tables of the experts' weight addresses"""
+def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shared_out, ffs=None, always_on=False):
+    """fp32 [N, W]: the chosen experts of a few tokens through tables of the experts' weight addresses.  ``ffs``: int32 sizes per
+    table entry (``ff`` = the largest); ``always_on``: table entry ``n_experts`` is an expert every token runs with weight 1"""
     h = _c(h)
     n, w = h.shape
     top = idx.shape[1]
-    act = torch.empty(max(n * top * ff, 1), dtype=h.dtype, device=h.device)
+    act = torch.empty(max(n * (top + int(always_on)) * ff, 1), dtype=h.dtype, device=h.device)
     y = torch.empty(n, w, dtype=torch.float32, device=h.device)
     native.call("mixers_moe_small", native.dtype_code(h.dtype), native.ptr(h), n, w, int(ff), top, int(n_experts), int(n_out), native.ptr(idx),
-                native.ptr(wgt), native.ptr(gate_up_table), native.ptr(down_table), native.ptr(shared_out), native.ptr(act), native.ptr(y),
-                native.stream(h.device))
+                native.ptr(wgt), native.ptr(gate_up_table), native.ptr(down_table), native.ptr(ffs), int(bool(always_on)), native.ptr(shared_out),
+                native.ptr(act), native.ptr(y), native.stream(h.device))
     return y
 
 

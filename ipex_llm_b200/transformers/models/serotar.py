@@ -128,17 +128,23 @@ class RoutedExperts(nn.Module):
         self._tables = None
 
     def address_tables(self, dtype, device):
-        """int64 device arrays of the experts' weight addresses, or None when the experts are not plain matrices of ``dtype``
-        (converted to a low-bit format); rebuilt when the weights moved"""
-        mods = [m for e in self.experts for m in (e.gate_up, e.down)]
-        if not mods or any(type(m) is not nn.Linear or m.weight.dtype != dtype or m.weight.device != device or not m.weight.is_contiguous()
-                           for m in mods):
+        """(gate_up addresses, down addresses, sizes, largest size, shared expert included?) as device arrays, or None when the
+        experts are not plain matrices of ``dtype`` (converted to a low-bit format); rebuilt when the weights moved.  A shared
+        expert that is a plain matrix too becomes the tables' last entry (the kernel runs it for every token)."""
+        def plain(mods):
+            return all(type(m) is nn.Linear and m.weight.dtype == dtype and m.weight.device == device and m.weight.is_contiguous() for m in mods)
+        experts = list(self.experts)
+        if not experts or not plain([m for e in experts for m in (e.gate_up, e.down)]):
             return None
-        key = (device, dtype, mods[0].weight.data_ptr(), mods[-1].weight.data_ptr())
+        with_shared = self.shared is not None and plain([self.shared.gate_up, self.shared.down])
+        if with_shared:
+            experts.append(self.shared)
+        key = (device, dtype, with_shared) + tuple(m.weight.data_ptr() for e in (experts[0], experts[-1]) for m in (e.gate_up, e.down))
         if self._tables is None or self._tables[0] != key:
             def table(ws):
                 return torch.tensor([w.weight.data_ptr() for w in ws], dtype=torch.int64, device=device)
-            self._tables = (key, table([e.gate_up for e in self.experts]), table([e.down for e in self.experts]))
+            ffs = torch.tensor([e.ff for e in experts], dtype=torch.int32, device=device)
+            self._tables = (key, table([e.gate_up for e in experts]), table([e.down for e in experts]), ffs, max(e.ff for e in experts), with_shared)
         return self._tables[1:]
 
 
@@ -227,9 +233,9 @@ class SerotarForCausalLM(PreTrainedModel, GenerationMixin):
         if S <= ABSORB_MAX_TOKENS:
             # few new tokens: score = (W_uk^T q) . c and out = W_uv (sum p c): the cache itself is key and value of one shared head
             wk, wv = w[:H * D].view(H, D, R), w[H * D:].view(H, Dv, R)
-            qa = torch.matmul(q.view(N, H, D).transpose(0, 1), wk).transpose(0, 1).contiguous()      # [N, H, R]
+            qa = torch.matmul(q.view(N, H, D).transpose(0, 1), wk).transpose(0, 1)                   # [N, H, R], stored head by head
             lat = store.unsqueeze(2)                                         # [B, capacity, 1, R]
-            o_lat = ops.softmax_attention(qa.view(N, H * R), lat, lat, B, S, H, held, 0, cache.pad, 0, mx.scale, dyn=dyn)
+            o_lat = ops.softmax_attention(qa, lat, lat, B, S, H, held, 0, cache.pad, 0, mx.scale, dyn=dyn)
             o = torch.matmul(o_lat.view(N, H, R).transpose(0, 1), wv.transpose(1, 2)).transpose(0, 1).reshape(N, H * Dv)
         else:
             # a prompt or a long portion: keys and values of every position so far, expanded from the latents
@@ -242,11 +248,13 @@ class SerotarForCausalLM(PreTrainedModel, GenerationMixin):
 
     def _experts(self, mlp, h, frozen_step):
         idx, wgt = ops.grouped_router(h, mlp.router, mlp.correction, mlp.groups, mlp.keep, mlp.top)
-        shared = mlp.shared(h) if mlp.shared is not None else None
         N, E = h.shape[0], mlp.n_experts
         tables = mlp.address_tables(h.dtype, h.device) if (N <= MOE_SMALL_TOKENS or frozen_step) else None
         if tables is not None:
-            return ops.moe_small(h, idx, wgt, tables[0], tables[1], mlp.ff, E, mlp.n_out, shared)
+            gate_up, down, ffs, ff_max, with_shared = tables
+            shared = mlp.shared(h) if (mlp.shared is not None and not with_shared) else None
+            return ops.moe_small(h, idx, wgt, gate_up, down, ff_max, E, mlp.n_out, shared, ffs=ffs, always_on=with_shared)
+        shared = mlp.shared(h) if mlp.shared is not None else None
         # many tokens: the (token, choice) pairs sorted by expert, one pair of matrix products per expert on its rows
         flat = idx.reshape(-1).to(torch.int64)
         order = torch.argsort(flat, stable=True)

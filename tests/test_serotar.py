@@ -74,8 +74,14 @@ CONFIGS = {
     # input as wide as a head
     "tile": dict(width=64, vocab=83, heads=4, dim=32, vdim=16, q_rank=24, kv_rank=64, kinds=("moe", "moe", "dense"), experts=6,
                  identity=2, groups=(2, 1), top=4, expert_ff=24, shared_ff=8, side_dim=16, bigram=(7, 5, 3)),
+    # head sizes and ranks that tile into nothing (24, 40, 100, 12), five heads, sixteen experts in four groups of which two are
+    # kept, no identity experts, a layer without feed-forward first, a side input of three channels
+    "wide": dict(width=72, vocab=300, heads=5, dim=24, vdim=40, q_rank=12, kv_rank=100, scale=0.15, ff=56, kinds=(None, "moe", "dense", "moe"),
+                 experts=16, identity=0, groups=(4, 2), top=3, expert_ff=8, shared_ff=40, side_dim=3, bigram=(211, 3, 1000003), emb_scale=1.3),
+    # no side input while the depth average is on: a layer's last addition is then the feed-forward's, or the mixer's own
+    "bare": dict(width=40, vocab=50, heads=4, dim=16, vdim=32, q_rank=16, kv_rank=128, kinds=(None, "dense", None), side_dim=0, bigram=(17, 1, 1)),
 }
-OPTIONS = {"plain": dict(layer_scale=False, depth_average=False)}
+OPTIONS = {"plain": dict(layer_scale=False, depth_average=False), "bare": dict(layer_scale=False)}
 
 
 def make(name, seed=0):
