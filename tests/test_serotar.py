@@ -607,6 +607,26 @@ def test_greedy_generate_matches_the_oracle(tmp_path, cuda_device, monkeypatch, 
 
 
 @pytest.mark.gpu
+def test_recorded_step_of_a_16_bit_model_equals_the_eager_loop(tmp_path, cuda_device, monkeypatch):
+    """a bf16 model whose decoding attention is the one-pass kernel over the latent cache (4 heads on a latent of 128): the
+    replayed step reads the cache length from the device and must produce the tokens of the loop that passes it from the host"""
+    cfg, w, model = build(tmp_path, "bare", torch.bfloat16, cuda_device)
+    prompts = torch.tensor([tokens_for(cfg, 70, 1), [0] * 30 + tokens_for(cfg, 40, 2)], device=cuda_device)
+    mask = torch.tensor([[1] * 70, [0] * 30 + [1] * 40], device=cuda_device)
+    replayed = model.generate(prompts, attention_mask=mask, max_new_tokens=80, do_sample=False)
+    assert model.__dict__.get("_b200_state_graph_failed") is None and model.__dict__.get("_b200_state_graphs")
+    monkeypatch.setenv("IPEX_LLM_B200_DECODE_GRAPH", "0")
+    eager = model.generate(prompts, attention_mask=mask, max_new_tokens=80, do_sample=False)
+    assert torch.equal(replayed, eager)
+    # and both follow the plain statement as far as a 16-bit model can: the first new token of each row
+    for b, n in ((0, 70), (1, 40)):
+        want = O.forward(cfg, w, prompts[b, 70 - n:].tolist())[-1]
+        top2 = want.topk(2).values
+        if top2[0] - top2[1] > 0.5:
+            assert int(replayed[b, 70]) == int(want.argmax())
+
+
+@pytest.mark.gpu
 def test_low_bit_conversion_runs_the_same_model(tmp_path, cuda_device, native_lib):
     """the projections are ordinary linears to the converter: a sym_int4 model answers close to the 16-bit one, its experts
     (no longer plain matrices) take the sorted path also for one token"""
