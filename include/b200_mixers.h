@@ -142,6 +142,11 @@ int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, i
                      const float* wgt, const int64_t* gate_up, const int64_t* down, const int32_t* ffs, int always_on,
                      const void* shared_out, void* act, float* y, mixers_stream_t stream);
 
+/* Counting sort of n_pairs = n_rows * top (token, choice) pairs by chosen output idx[i] in [0, n_keys): counts[e] = pairs of e;
+ * pos[i] = row of pair i among the sorted pairs; token_of[row] = i / top. */
+int mixers_moe_sort(const int32_t* idx, long n_pairs, int top, int n_keys, int32_t* counts, int32_t* pos, int64_t* token_of,
+                    mixers_stream_t stream);
+
 /* y float [n_rows, width] = sum_k w[n, k] * rows[pos[n, k], :] for chosen e < n_experts, w * h[n, :] for identity experts,
  * + shared_out; rows: dtype [*, width], the experts' outputs on rows sorted by expert. */
 int mixers_moe_combine(int dtype, const void* rows, const int32_t* pos, const int32_t* idx, const float* wgt, const void* h,

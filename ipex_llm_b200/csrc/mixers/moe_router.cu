@@ -4,7 +4,8 @@
 //     eligible; weights = the winners' softmax scores;
 //   moe_small_up / moe_small_down: the chosen experts of a few tokens straight from the experts' weight matrices (device
 //     tables of addresses), nothing on the host between router and result: the path of decoding and of a recorded step;
-//   moe_combine: the weighted sum of expert outputs that were computed expert by expert on sorted rows (many tokens).
+//   moe_sort / moe_combine: many tokens -- the (token, choice) pairs counted and sorted by expert on the device, then the
+//     weighted sum of the expert outputs that were computed expert by expert on the sorted rows.
 // Outputs numbered >= n_experts are identity experts: their output is the token's input itself.
 #include "mixers_common.cuh"
 #include <math.h>
@@ -160,6 +161,31 @@ __global__ void __launch_bounds__(256) moe_small_down_kernel(const T* __restrict
     if (lane == 0) y[n * width + c] = sum;
 }
 
+// Counting sort of the (token, choice) pairs by chosen output, one block: counts[e] = pairs that chose e, pos[i] = row of pair i
+// among the pairs sorted by output, token_of[row] = the pair's token.  The order inside one output's rows is whatever the atomic
+// counters hand out; every row is computed on its own, so the result does not depend on it.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restrict__ idx, long n_pairs, int top, int n_keys, int32_t* __restrict__ counts,
+                                                        int32_t* __restrict__ pos, int64_t* __restrict__ token_of) {
+    extern __shared__ int sort_sh[];                        // counts [n_keys], then running offsets [n_keys]
+    int* cnt = sort_sh;
+    int* off = sort_sh + n_keys;
+    for (int e = threadIdx.x; e < n_keys; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (long i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_keys; ++e) { off[e] = run; run += cnt[e]; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_keys; e += blockDim.x) counts[e] = cnt[e];
+    for (long i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int p = atomicAdd(&off[idx[i]], 1);
+        pos[i] = p;
+        token_of[p] = i / top;
+    }
+}
+
 // y[n, c] = sum_k w[n, k] * rows[pos[n, k], c] (identity experts: w * h[n, c]) + shared[n, c]
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ pos, const int32_t* __restrict__ idx,
@@ -218,5 +244,14 @@ extern "C" int mixers_moe_combine(int dtype, const void* rows, const int32_t* po
     if (blocks > 148L * 16) blocks = 148L * 16;
     MIXERS_DISPATCH(dtype, moe_combine_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
         (const T*)rows, pos, idx, wgt, (const T*)h, (const T*)shared_out, n_rows, width, top, n_experts, n_out, y));
+    return mixers_status();
+}
+
+extern "C" int mixers_moe_sort(const int32_t* idx, long n_pairs, int top, int n_keys, int32_t* counts, int32_t* pos, int64_t* token_of,
+                               mixers_stream_t stream) {
+    if (n_pairs <= 0) return 0;
+    size_t smem = 2 * (size_t)n_keys * sizeof(int);
+    if (n_keys < 1 || smem > 48 * 1024 || top < 1) return (int)cudaErrorInvalidValue;
+    moe_sort_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>(idx, n_pairs, top, n_keys, counts, pos, token_of);
     return mixers_status();
 }

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "mixers_grouped_router": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_small": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
                          _c_ptr, _c_ptr, _c_ptr],
+    "mixers_moe_sort": [_c_ptr, _c_long, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_combine": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
 }
 

@@ -262,6 +262,18 @@ def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shar
     return y
 
 
+def moe_sort(idx, n_keys):
+    """(counts int32 [n_keys], pos int32 [N, top], token_of int64 [N * top]): the (token, choice) pairs sorted by chosen output"""
+    idx = _c(idx)
+    n, top = idx.shape
+    counts = torch.empty(n_keys, dtype=torch.int32, device=idx.device)
+    pos = torch.empty(n, top, dtype=torch.int32, device=idx.device)
+    token_of = torch.empty(n * top, dtype=torch.int64, device=idx.device)
+    native.call("mixers_moe_sort", native.ptr(idx), n * top, top, int(n_keys), native.ptr(counts), native.ptr(pos), native.ptr(token_of),
+                native.stream(idx.device))
+    return counts, pos, token_of
+
+
 def moe_combine(rows, pos, idx, wgt, h, shared_out, n_experts, n_out):
     """fp32 [N, W]: weighted sum of the experts' outputs ``rows`` (row pos[n, k] belongs to token n's k-th choice)"""
     h = _c(h)

@@ -255,18 +255,20 @@ class SerotarForCausalLM(PreTrainedModel, GenerationMixin):
             shared = mlp.shared(h) if (mlp.shared is not None and not with_shared) else None
             return ops.moe_small(h, idx, wgt, gate_up, down, ff_max, E, mlp.n_out, shared, ffs=ffs, always_on=with_shared)
         shared = mlp.shared(h) if mlp.shared is not None else None
-        # many tokens: the (token, choice) pairs sorted by expert, one pair of matrix products per expert on its rows
-        flat = idx.reshape(-1).to(torch.int64)
-        order = torch.argsort(flat, stable=True)
-        pos = torch.empty(flat.shape[0], dtype=torch.int32, device=h.device)
-        pos[order] = torch.arange(flat.shape[0], dtype=torch.int32, device=h.device)
-        counts = torch.bincount(flat, minlength=mlp.n_out + 1)[:E].tolist()
-        token_of = torch.div(order, mlp.top, rounding_mode="floor")
+        # many tokens: the (token, choice) pairs sorted by expert on the device, one pair of matrix products per expert on its rows
+        # (the counts are read on the host: the one synchronisation of the layer)
+        counts, pos, token_of = ops.moe_sort(idx, mlp.n_out + 1)
+        counts = counts[:E].tolist()
         rows = torch.empty(max(sum(counts), 1), h.shape[1], dtype=h.dtype, device=h.device)
         off = 0
         for e, cnt in enumerate(counts):
             if cnt:
-                rows[off:off + cnt] = mlp.experts[e](h.index_select(0, token_of[off:off + cnt]))
+                expert = mlp.experts[e]
+                a = ops.silu_mul(expert.gate_up(h.index_select(0, token_of[off:off + cnt])), expert.ff)
+                if type(expert.down) is nn.Linear:
+                    torch.mm(a, expert.down.weight.t(), out=rows[off:off + cnt])             # straight into the sorted rows
+                else:
+                    rows[off:off + cnt] = expert.down(a)
                 off += cnt
         return ops.moe_combine(rows, pos, idx, wgt, h, shared, E, mlp.n_out)
 

@@ -461,6 +461,22 @@ def test_grouped_router(mixers, cuda_device, dtype, n_out, groups, keep, top, sh
     assert (got - want).abs().max() < 1e-5                                  # the router is 32-bit whatever the dtype
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,top,n_keys", [(1, 1, 2), (37, 3, 10), (5000, 4, 65), (300, 2, 1025)])
+def test_pairs_sorted_by_expert(mixers, cuda_device, n, top, n_keys):
+    g = torch.Generator().manual_seed(n)
+    idx = torch.randint(0, n_keys, (n, top), generator=g).to(torch.int32).to(cuda_device)
+    counts, pos, token_of = mixers.moe_sort(idx, n_keys)
+    flat = idx.reshape(-1).cpu().to(torch.int64)
+    assert torch.equal(counts.cpu().to(torch.int64), torch.bincount(flat, minlength=n_keys))
+    p = pos.reshape(-1).cpu().to(torch.int64)
+    assert torch.equal(p.sort().values, torch.arange(n * top))                                # a permutation
+    assert torch.equal(token_of.cpu()[p], torch.arange(n * top) // top)                       # every row knows its token
+    by_row = torch.empty(n * top, dtype=torch.int64)
+    by_row[p] = flat
+    assert torch.equal(by_row, flat.sort().values)                                            # rows are grouped by output, in order
+
+
 # ================================================================== GPU: the model
 def build(tmp_path, name, dtype, device, seed=0, **kw):
     cfg, w = make(name, seed)
