@@ -228,10 +228,11 @@ def test_pair_embedding(mixers, cuda_device, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [45, 1100])
-def test_residual_norm_and_depth_average(mixers, cuda_device, dtype, width):
+@pytest.mark.parametrize("width,n", [(45, 5), (1100, 5), (8200, 3), (40, 1100)])
+def test_residual_norm_and_depth_average(mixers, cuda_device, dtype, width, n):
+    """rows held in registers (few rows, up to 8192 wide) and the plain loop (wider rows; many rows under a depth average)"""
     g = torch.Generator().manual_seed(4)
-    n, eps = 5, 1e-3
+    eps = 1e-3
     x0 = torch.randn(n, width, generator=g)
     gain, vec = _rand((), g, dtype, cuda_device) + 1.5, _rand((width,), g, dtype, cuda_device)
     coef = _rand((3,), g, dtype, cuda_device)
@@ -282,7 +283,7 @@ def test_activations(mixers, cuda_device, dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_latent_prepare(mixers, cuda_device, dtype):
     g = torch.Generator().manual_seed(7)
-    B, S, qr, kr, held, cap, eps = 2, 3, 10, 13, 4, 9, 1e-4
+    B, S, qr, kr, held, cap, eps = 2, 3, 10, (13 if dtype == torch.float32 else 1100), 4, 9, 1e-4       # 1100: wider than the registers hold
     proj = _rand((B, S, 2 + qr + 3 + kr), g, dtype, cuda_device, 2.0)
     qw, cw = _rand((qr,), g, dtype, cuda_device), _rand((kr,), g, dtype, cuda_device)
     store = torch.full((B, cap, kr), 9.0, dtype=dtype, device=cuda_device)
